@@ -1,0 +1,82 @@
+// Activation functors used by the fused kernels.
+//
+// The reference turns every activation (id, forward snippet, adjoint snippet) into
+//   struct id { static __device__ half forward(half x); static __device__ half adjoint(half x, half adjz); };
+// (src_cpp/src/activation.cpp:13-40). The fused kernels here work on half2 pairs, so a functor exposes
+// forward2 / adjoint2. User snippets are wrapped by ScalarActivation; the four built-ins of
+// src_cpp/include/qmlp/builtin-activations.json:1-21 have hand-written half2 forms with the same semantics.
+#pragma once
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+// helpers user snippets may reference (src_cpp/include/qmlp/kernels/common.cuh:16-19)
+__device__ __forceinline__ half hZERO() { return __ushort_as_half(0); }
+
+namespace qmlp {
+namespace kernel {
+
+template <class A>
+struct ScalarActivation {
+    static __device__ __forceinline__ __half2 forward2(__half2 x)
+    {
+        return __halves2half2(A::forward(__low2half(x)), A::forward(__high2half(x)));
+    }
+    static __device__ __forceinline__ __half2 adjoint2(__half2 x, __half2 adjz)
+    {
+        return __halves2half2(A::adjoint(__low2half(x), __low2half(adjz)),
+                              A::adjoint(__high2half(x), __high2half(adjz)));
+    }
+    static __device__ __forceinline__ half forward(half x) { return A::forward(x); }
+    static __device__ __forceinline__ half adjoint(half x, half adjz) { return A::adjoint(x, adjz); }
+};
+
+__device__ __forceinline__ __half2 select_gt0(__half2 x, __half2 ifTrue, __half2 ifFalse)
+{
+    // per lane: x > 0 ? ifTrue : ifFalse (false for NaN, like __hgt)
+    uint32_t m = __hgt2_mask(x, __float2half2_rn(0.f));
+    uint32_t t = *reinterpret_cast<uint32_t*>(&ifTrue);
+    uint32_t f = *reinterpret_cast<uint32_t*>(&ifFalse);
+    uint32_t r = (t & m) | (f & ~m);
+    return *reinterpret_cast<__half2*>(&r);
+}
+
+// "z = __hgt(x, hZERO()) ? x : hZERO()" / "adjx = __hgt(x, hZERO()) ? adjz : hZERO()"
+struct BuiltinRelu {
+    static __device__ __forceinline__ __half2 forward2(__half2 x) { return select_gt0(x, x, __float2half2_rn(0.f)); }
+    static __device__ __forceinline__ __half2 adjoint2(__half2 x, __half2 adjz) { return select_gt0(x, adjz, __float2half2_rn(0.f)); }
+    static __device__ __forceinline__ half forward(half x) { return __hgt(x, hZERO()) ? x : hZERO(); }
+    static __device__ __forceinline__ half adjoint(half x, half adjz) { return __hgt(x, hZERO()) ? adjz : hZERO(); }
+};
+
+// "z = __hgt(x, hZERO()) ? x : __hsub(hexp(x), 1)" / "adjx = __hgt(x, hZERO()) ? adjz : __hmul(adjz, hexp(x))"
+struct BuiltinCelu {
+    static __device__ __forceinline__ __half2 forward2(__half2 x)
+    {
+        return select_gt0(x, x, __hsub2(h2exp(x), __float2half2_rn(1.0f)));
+    }
+    static __device__ __forceinline__ __half2 adjoint2(__half2 x, __half2 adjz)
+    {
+        return select_gt0(x, adjz, __hmul2(adjz, h2exp(x)));
+    }
+    static __device__ __forceinline__ half forward(half x) { return __hgt(x, hZERO()) ? x : __hsub(hexp(x), __float2half(1.0f)); }
+    static __device__ __forceinline__ half adjoint(half x, half adjz) { return __hgt(x, hZERO()) ? adjz : __hmul(adjz, hexp(x)); }
+};
+
+// "z = hsin(x)" / "adjx = __hmul(hcos(x), adjz)"
+struct BuiltinSine {
+    static __device__ __forceinline__ __half2 forward2(__half2 x) { return h2sin(x); }
+    static __device__ __forceinline__ __half2 adjoint2(__half2 x, __half2 adjz) { return __hmul2(h2cos(x), adjz); }
+    static __device__ __forceinline__ half forward(half x) { return hsin(x); }
+    static __device__ __forceinline__ half adjoint(half x, half adjz) { return __hmul(hcos(x), adjz); }
+};
+
+// "z = x" / "adjx = adjz"
+struct BuiltinIdentity {
+    static __device__ __forceinline__ __half2 forward2(__half2 x) { return x; }
+    static __device__ __forceinline__ __half2 adjoint2(__half2, __half2 adjz) { return adjz; }
+    static __device__ __forceinline__ half forward(half x) { return x; }
+    static __device__ __forceinline__ half adjoint(half, half adjz) { return adjz; }
+};
+
+} // namespace kernel
+} // namespace qmlp

@@ -1,0 +1,746 @@
+// Fused network kernels: encodings -> fully-connected layer chain, forward and adjoint.
+//
+// They replace the reference's NetworkKernelInferenceAndForward (src_cpp/include/qmlp/kernels/network_forward.cuh:34-114),
+// NetworkKernelBackward (kernels/network_backward.cuh:33-114) and Layer<>::inference/adjoint (kernels/layer.cuh:101-265).
+//
+// Design (not the reference's): a persistent grid; every CTA stages all weight matrices and biases of the network
+// in shared memory once; every warp then works alone on tiles of 32 points. The activations of a tile never leave
+// registers between layers: the fp32 accumulator fragment of one m16n8k16 MMA, rounded to half2 and passed through
+// the activation, is exactly the A-operand fragment of the next layer. Weights are read from shared memory with
+// ldmatrix (forward) and ldmatrix.trans (adjoint, W^T) from one row-major copy. Accumulation is fp32 (the reference
+// accumulates in half).
+//
+// A `Spec` type, generated per network, supplies the compile-time geometry:
+//   NUM_INPUTS, NUM_OUTPUTS, NUM_LAYERS, ENC_CHANNELS, NUM_ENCODINGS, WARPS, MIN_BLOCKS
+//   CIN[l], COUT[l] (padded to 16), WOFF[l], BOFF[l] (-1: no bias)   -- offsets into the flat parameter vector
+//   template<int L> struct Act  : activation functor of layer L
+//   template<int E> struct Enc  : EncIdentity<...> or EncGrid<...>
+#pragma once
+#include "launch_args.h"
+#include "mma.cuh"
+#include "activations.cuh"
+#include "grid.cuh"
+
+namespace qmlp {
+namespace kernel {
+
+constexpr int TILE_POINTS = 32; // points per warp tile = 2 MMA row tiles
+constexpr int MT = 2;
+
+// ---- encoding descriptors ------------------------------------------------------------------------------------
+template <int START_, int N_, int OUT_OFF_>
+struct EncIdentity {
+    static constexpr bool IS_GRID = false;
+    static constexpr int START = START_, N = N_, OUT_OFF = OUT_OFF_, NUM_OUT = N_;
+};
+template <int START_, int D_, int L_, int F_, bool CONCAT_, int OUT_OFF_, int SLOT_, bool HALF_TABLE_>
+struct EncGrid {
+    static constexpr bool IS_GRID = true;
+    static constexpr int START = START_, D = D_, L = L_, F = F_, OUT_OFF = OUT_OFF_, SLOT = SLOT_;
+    static constexpr bool CONCAT = CONCAT_, HALF_TABLE = HALF_TABLE_;
+    static constexpr int NUM_OUT = CONCAT_ ? L_ * F_ : F_;
+};
+
+// ---- shared memory layout ------------------------------------------------------------------------------------
+// weights of layer l: [COUT][CIN + 8] halfs (row padded by 16 bytes: conflict-free ldmatrix), then fp32 biases,
+// then one [32][CIN0 + 8] half tile per warp.
+template <class Spec>
+struct SmemLayout {
+    static constexpr int NL = Spec::NUM_LAYERS;
+    __host__ __device__ static constexpr int wStride(int l) { return Spec::CIN[l] + 8; }
+    __host__ __device__ static constexpr int wOffsetHalfs(int l)
+    {
+        int o = 0;
+        for (int i = 0; i < l; ++i) o += Spec::COUT[i] * (Spec::CIN[i] + 8);
+        return o;
+    }
+    __host__ __device__ static constexpr int weightHalfs() { return wOffsetHalfs(NL); }
+    __host__ __device__ static constexpr int biasOffsetFloats(int l)
+    {
+        int o = 0;
+        for (int i = 0; i < l; ++i) o += Spec::COUT[i];
+        return o;
+    }
+    __host__ __device__ static constexpr int biasFloats() { return biasOffsetFloats(NL); }
+    __host__ __device__ static constexpr int biasStartBytes() { return ((weightHalfs() * 2 + 15) / 16) * 16; }
+    __host__ __device__ static constexpr int tileStride() { return Spec::CIN[0] + 8; }
+    __host__ __device__ static constexpr int tileStartBytes() { return ((biasStartBytes() + biasFloats() * 4 + 15) / 16) * 16; }
+    __host__ __device__ static constexpr int tileBytesPerWarp() { return TILE_POINTS * tileStride() * 2; }
+    __host__ __device__ static constexpr int totalBytes() { return tileStartBytes() + Spec::WARPS * tileBytesPerWarp(); }
+    // prefix sums of the stash (in halfs per point)
+    __host__ __device__ static constexpr int preOffset(int l)
+    { // encoded input first, then the pre-activations of every layer
+        int o = Spec::CIN[0];
+        for (int i = 0; i < l; ++i) o += Spec::COUT[i];
+        return o;
+    }
+    __host__ __device__ static constexpr int deltaOffset(int l)
+    {
+        int o = 0;
+        for (int i = 0; i < l; ++i) o += Spec::COUT[i];
+        return o;
+    }
+};
+
+template <class Spec, int L>
+__device__ __forceinline__ void stage_layer(const LaunchArgs& p, __half* sW, float* sB)
+{
+    if constexpr (L < Spec::NUM_LAYERS) {
+        using SL = SmemLayout<Spec>;
+        constexpr int CIN = Spec::CIN[L], COUT = Spec::COUT[L];
+        constexpr int CHUNKS = CIN / 8; // 16-byte chunks per row
+        const __half* gW = p.weights + Spec::WOFF[L];
+        __half* dW = sW + SL::wOffsetHalfs(L);
+        for (int i = threadIdx.x; i < COUT * CHUNKS; i += blockDim.x) {
+            const int r = i / CHUNKS, c = i % CHUNKS;
+            const uint4 v = *reinterpret_cast<const uint4*>(gW + r * CIN + c * 8);
+            *reinterpret_cast<uint4*>(dW + r * SL::wStride(L) + c * 8) = v;
+        }
+        float* dB = sB + SL::biasOffsetFloats(L);
+        for (int i = threadIdx.x; i < COUT; i += blockDim.x)
+            dB[i] = Spec::BOFF[L] >= 0 ? __half2float(p.weights[(Spec::BOFF[L] >= 0 ? Spec::BOFF[L] : 0) + i]) : 0.f;
+        stage_layer<Spec, L + 1>(p, sW, sB);
+    }
+}
+
+// ---- encodings (one lane = one point of the warp tile) ---------------------------------------------------------
+struct RowReader {
+    const float* base; // already offset to the point's row
+    long long s1;
+    __device__ __forceinline__ float operator()(int c) const { return __ldg(base + c * s1); }
+};
+
+struct HalfRowWriter { // one row of the warp's shared-memory tile
+    __half* row;
+    __device__ __forceinline__ void operator()(int c, float v) const { row[c] = __float2half(v); }
+};
+struct HalfRowReader {
+    const __half* row;
+    __device__ __forceinline__ float operator()(int c) const { return __half2float(row[c]); }
+};
+
+template <class Spec, int E, class Out>
+__device__ __forceinline__ void encode_point(const LaunchArgs& p, const RowReader& in, const Out& out)
+{
+    if constexpr (E < Spec::NUM_ENCODINGS) {
+        using Enc = typename Spec::template Enc<E>;
+        if constexpr (!Enc::IS_GRID) {
+            // src_cpp/include/qmlp/kernels/encoding_identity.cuh:16-25
+#pragma unroll
+            for (int i = 0; i < Enc::N; ++i) out(Enc::OUT_OFF + i, in(i + Enc::START));
+        } else {
+            const GridP& g = p.grids[Enc::SLOT];
+            float pos[Enc::D];
+            grid_position<Enc::D, Enc::START>(g, in, pos);
+            if constexpr (Enc::CONCAT) {
+#pragma unroll 2
+                for (int l = 0; l < Enc::L; ++l) {
+                    float feat[Enc::F];
+                    grid_level_forward<Enc::D, Enc::F, Enc::HALF_TABLE>(g, g.levels[l], pos, feat);
+#pragma unroll
+                    for (int i = 0; i < Enc::F; ++i) out(Enc::OUT_OFF + l * Enc::F + i, feat[i]);
+                }
+            } else {
+                // "add": the reference accumulates the half outputs level by level (encoding_hashgrid.cuh:330-335)
+                float acc[Enc::F];
+#pragma unroll
+                for (int i = 0; i < Enc::F; ++i) acc[i] = 0.f;
+                for (int l = 0; l < Enc::L; ++l) {
+                    float feat[Enc::F];
+                    grid_level_forward<Enc::D, Enc::F, Enc::HALF_TABLE>(g, g.levels[l], pos, feat);
+#pragma unroll
+                    for (int i = 0; i < Enc::F; ++i) acc[i] += feat[i];
+                }
+#pragma unroll
+                for (int i = 0; i < Enc::F; ++i) out(Enc::OUT_OFF + i, acc[i]);
+            }
+        }
+        encode_point<Spec, E + 1, Out>(p, in, out);
+    }
+}
+
+// ---- forward layer chain -------------------------------------------------------------------------------------
+// MODE 0: inference, 1: forward with stash, 2: forward with stash + L2 loss gradient instead of the output
+template <class Spec, int L, int MODE>
+__device__ __forceinline__ void forward_layers(const LaunchArgs& p, const __half* sW, const float* sB,
+                                               uint32_t (&aIn)[MT][Spec::CIN[L] / 16][4], long long rowBase, long long n32,
+                                               float& lossAcc)
+{
+    using SL = SmemLayout<Spec>;
+    using Act = typename Spec::template Act<L>;
+    constexpr int CIN = Spec::CIN[L], COUT = Spec::COUT[L];
+    constexpr int KT = CIN / 16, NC = COUT / 16;
+    constexpr bool LAST = (L == Spec::NUM_LAYERS - 1);
+    constexpr int WS = SL::wStride(L);
+    const int lane = threadIdx.x & 31;
+    const int r = lane >> 2, q = lane & 3;
+    const __half* w = sW + SL::wOffsetHalfs(L);
+    const float* bias = sB + SL::biasOffsetFloats(L);
+    // ldmatrix lane address of the B fragments: two n8 tiles x (k 0-7, k 8-15)
+    const uint32_t wAddr = smem_u32(w + ((lane & 7) + ((lane >> 4) << 3)) * WS + ((lane >> 3) & 1) * 8);
+
+    uint32_t aOut[MT][LAST ? 1 : NC][4];
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+        if constexpr (LAST) {
+            if (j * 16 >= Spec::NUM_OUTPUTS) continue; // padded output channels are never read
+        }
+        float acc[MT][2][4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float b0 = bias[j * 16 + h * 8 + q * 2], b1 = bias[j * 16 + h * 8 + q * 2 + 1];
+#pragma unroll
+            for (int m = 0; m < MT; ++m) { acc[m][h][0] = b0; acc[m][h][1] = b1; acc[m][h][2] = b0; acc[m][h][3] = b1; }
+        }
+#pragma unroll
+        for (int k = 0; k < KT; ++k) {
+            uint32_t b[4];
+            ldmatrix_x4(b, wAddr + (j * 16 * WS + k * 16) * 2);
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                mma16816(acc[m][0], aIn[m][k], b[0], b[1]);
+                mma16816(acc[m][1], aIn[m][k], b[2], b[3]);
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const __half2 lo = __floats2half2_rn(acc[m][h][0], acc[m][h][1]); // row r
+                const __half2 hi = __floats2half2_rn(acc[m][h][2], acc[m][h][3]); // row r + 8
+                const long long row0 = rowBase + m * 16 + r;
+                const int col = j * 16 + h * 8 + q * 2;
+                if constexpr (MODE >= 1) {
+                    // pre-activation stash, row-major (N32, COUT) per layer (reference: kernels/layer.cuh:156-163)
+                    __half* st = p.fwdTmp + n32 * SL::preOffset(L);
+                    if (row0 < p.numel) *reinterpret_cast<__half2*>(st + row0 * COUT + col) = lo;
+                    if (row0 + 8 < p.numel) *reinterpret_cast<__half2*>(st + (row0 + 8) * COUT + col) = hi;
+                }
+                const __half2 zlo = Act::forward2(lo), zhi = Act::forward2(hi);
+                if constexpr (!LAST) {
+                    aOut[m][j][h * 2 + 0] = h2_as_u32(zlo);
+                    aOut[m][j][h * 2 + 1] = h2_as_u32(zhi);
+                } else {
+                    // first NUM_OUTPUTS channels -> fp32 (kernels/network_forward.cuh:103-111)
+                    const float2 flo = __half22float2(zlo), fhi = __half22float2(zhi);
+                    const float v[4] = {flo.x, flo.y, fhi.x, fhi.y};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const long long row = row0 + (e >> 1) * 8;
+                        const int c = col + (e & 1);
+                        if (c < Spec::NUM_OUTPUTS && row < p.numel) {
+                            if constexpr (MODE == 2) {
+                                const float d = v[e] - __ldg(p.target + row * p.tS0 + c * p.tS1);
+                                lossAcc += d * d;
+                                p.output[row * p.outS0 + c * p.outS1] = p.lossScale * d;
+                            } else {
+                                p.output[row * p.outS0 + c * p.outS1] = v[e];
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if constexpr (!LAST) forward_layers<Spec, L + 1, MODE>(p, sW, sB, aOut, rowBase, n32, lossAcc);
+}
+
+template <class Spec, int MODE>
+__global__ void __launch_bounds__(Spec::WARPS * 32, Spec::MIN_BLOCKS)
+fused_forward_kernel(const __grid_constant__ LaunchArgs p)
+{
+    using SL = SmemLayout<Spec>;
+    extern __shared__ __align__(16) unsigned char smem[];
+    __half* sW = reinterpret_cast<__half*>(smem);
+    float* sB = reinterpret_cast<float*>(smem + SL::biasStartBytes());
+    stage_layer<Spec, 0>(p, sW, sB);
+    __syncthreads();
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __half* tile = reinterpret_cast<__half*>(smem + SL::tileStartBytes() + warp * SL::tileBytesPerWarp());
+    constexpr int TS = SL::tileStride();
+    constexpr int CIN0 = Spec::CIN[0];
+    const long long n32 = (p.numel + 31) / 32 * 32;
+    const long long numTiles = n32 / TILE_POINTS;
+    float lossAcc = 0.f;
+
+    for (long long t = static_cast<long long>(blockIdx.x) * Spec::WARPS + warp; t < numTiles;
+         t += static_cast<long long>(gridDim.x) * Spec::WARPS) {
+        const long long rowBase = t * TILE_POINTS;
+        const long long myRow = rowBase + lane;
+        __half* row = tile + lane * TS;
+        // encodings; padding channels and invalid tail points are zero (kernels/network_forward.cuh:67-89)
+        if (myRow < p.numel) {
+            RowReader in{p.input + myRow * p.inS0, p.inS1};
+            encode_point<Spec, 0>(p, in, HalfRowWriter{row});
+#pragma unroll
+            for (int c = Spec::ENC_CHANNELS; c < CIN0; ++c) row[c] = __ushort_as_half(0);
+        } else {
+#pragma unroll
+            for (int c = 0; c < CIN0; c += 8) *reinterpret_cast<uint4*>(row + c) = make_uint4(0, 0, 0, 0);
+        }
+        __syncwarp();
+        if constexpr (MODE >= 1) {
+            // stash the encoded input: the layer-0 weight gradient reads it instead of re-running the encodings
+            constexpr int CH = CIN0 / 8;
+            __half* st = p.fwdTmp; // offset 0
+            for (int i = lane; i < TILE_POINTS * CH; i += 32) {
+                const int rr = i / CH, cc = i % CH;
+                if (rowBase + rr < p.numel)
+                    *reinterpret_cast<uint4*>(st + (rowBase + rr) * CIN0 + cc * 8) = *reinterpret_cast<const uint4*>(tile + rr * TS + cc * 8);
+            }
+        }
+        uint32_t a0[MT][CIN0 / 16][4];
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+#pragma unroll
+            for (int k = 0; k < CIN0 / 16; ++k)
+                ldmatrix_x4(a0[m][k], smem_u32(tile + (m * 16 + (lane & 15)) * TS + k * 16 + (lane >> 4) * 8));
+        __syncwarp();
+        forward_layers<Spec, 0, MODE>(p, sW, sB, a0, rowBase, n32, lossAcc);
+    }
+    if constexpr (MODE == 2) {
+        if (p.lossSum != nullptr) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) lossAcc += __shfl_xor_sync(0xffffffffu, lossAcc, o);
+            if (lane == 0 && lossAcc != 0.f) atomicAdd(p.lossSum, lossAcc);
+        }
+    }
+}
+
+// ---- adjoint -------------------------------------------------------------------------------------------------
+template <class Spec, int E, bool INPUT_GRAD, bool PARAM_GRAD, class AdjOut>
+__device__ __forceinline__ void encode_adjoint_point(const LaunchArgs& p, const RowReader& in, const AdjOut& adjOut,
+                                                     float* adjInRow, long long aiS1)
+{
+    if constexpr (E < Spec::NUM_ENCODINGS) {
+        using Enc = typename Spec::template Enc<E>;
+        if constexpr (!Enc::IS_GRID) {
+            // src_cpp/include/qmlp/kernels/encoding_identity.cuh:27-38
+            if constexpr (INPUT_GRAD) {
+#pragma unroll
+                for (int i = 0; i < Enc::N; ++i) adjInRow[(i + Enc::START) * aiS1] += adjOut(Enc::OUT_OFF + i);
+            }
+        } else {
+            const GridP& g = p.grids[Enc::SLOT];
+            const bool paramGrad = PARAM_GRAD && g.grad != nullptr;
+            float pos[Enc::D], adjPos[Enc::D];
+            grid_position<Enc::D, Enc::START>(g, in, pos);
+#pragma unroll
+            for (int k = 0; k < Enc::D; ++k) adjPos[k] = 0.f;
+            for (int l = 0; l < Enc::L; ++l) {
+                float adjF[Enc::F];
+#pragma unroll
+                for (int i = 0; i < Enc::F; ++i) adjF[i] = adjOut(Enc::OUT_OFF + (Enc::CONCAT ? l * Enc::F : 0) + i);
+                if (paramGrad)
+                    grid_level_adjoint<Enc::D, Enc::F, Enc::HALF_TABLE, true, INPUT_GRAD>(g, g.levels[l], pos, adjF, adjPos);
+                else if constexpr (INPUT_GRAD)
+                    grid_level_adjoint<Enc::D, Enc::F, Enc::HALF_TABLE, false, true>(g, g.levels[l], pos, adjF, adjPos);
+            }
+            if constexpr (INPUT_GRAD) {
+                // encoding_hashgrid.cuh:414-421
+#pragma unroll
+                for (int k = 0; k < Enc::D; ++k) adjInRow[(k + Enc::START) * aiS1] += adjPos[k] * g.boxInvSize[k];
+            }
+        }
+        encode_adjoint_point<Spec, E + 1, INPUT_GRAD, PARAM_GRAD, AdjOut>(p, in, adjOut, adjInRow, aiS1);
+    }
+}
+
+// FLAGS: FLAG_GRAD_INPUT | FLAG_GRAD_WEIGHTS | FLAG_GRAD_ENCODINGS
+template <class Spec, int L, int FLAGS>
+__device__ __forceinline__ void backward_layers(const LaunchArgs& p, const __half* sW,
+                                                uint32_t (&adj)[MT][Spec::COUT[L] / 16][4], long long rowBase,
+                                                long long n32, __half* tile)
+{
+    using SL = SmemLayout<Spec>;
+    using Act = typename Spec::template Act<L>;
+    constexpr int CIN = Spec::CIN[L], COUT = Spec::COUT[L];
+    constexpr int KT = COUT / 16, NC = CIN / 16;
+    constexpr int WS = SL::wStride(L);
+    constexpr bool NEED_ENC = (FLAGS & (FLAG_GRAD_INPUT | FLAG_GRAD_ENCODINGS)) != 0;
+    const int lane = threadIdx.x & 31;
+    const int r = lane >> 2, q = lane & 3;
+
+    // delta = Act'(pre) * adj, in place (kernels/layer.cuh:216-229), pre-activations read back in fragment layout
+    const __half* pre = p.fwdTmp + n32 * SL::preOffset(L);
+    __half* dl = p.adjTmp + n32 * SL::deltaOffset(L);
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int k = 0; k < KT; ++k)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const long long row = rowBase + m * 16 + r + (e & 1) * 8;
+                const int col = k * 16 + (e >> 1) * 8 + q * 2;
+                __half2 x = __float2half2_rn(0.f);
+                if (row < p.numel) x = *reinterpret_cast<const __half2*>(pre + row * COUT + col);
+                const __half2 d = Act::adjoint2(x, u32_as_h2(adj[m][k][e]));
+                adj[m][k][e] = h2_as_u32(d);
+                if constexpr ((FLAGS & FLAG_GRAD_WEIGHTS) != 0) {
+                    if (row < p.numel) *reinterpret_cast<__half2*>(dl + row * COUT + col) = d;
+                }
+            }
+
+    if constexpr (L > 0 || NEED_ENC) {
+        // adjIn (points x CIN) = delta (points x COUT) * W (COUT x CIN): B fragments by transposing ldmatrix
+        const __half* w = sW + SL::wOffsetHalfs(L);
+        const uint32_t wAddr = smem_u32(w + ((lane & 7) + ((lane >> 3) & 1) * 8) * WS + (lane >> 4) * 8);
+        uint32_t adjIn[MT][NC][4];
+#pragma unroll
+        for (int j = 0; j < NC; ++j) {
+            float acc[MT][2][4];
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[m][h][e] = 0.f;
+#pragma unroll
+            for (int k = 0; k < KT; ++k) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, wAddr + (k * 16 * WS + j * 16) * 2);
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    mma16816(acc[m][0], adj[m][k], b[0], b[1]);
+                    mma16816(acc[m][1], adj[m][k], b[2], b[3]);
+                }
+            }
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    adjIn[m][j][h * 2 + 0] = h2_as_u32(__floats2half2_rn(acc[m][h][0], acc[m][h][1]));
+                    adjIn[m][j][h * 2 + 1] = h2_as_u32(__floats2half2_rn(acc[m][h][2], acc[m][h][3]));
+                }
+        }
+        if constexpr (L > 0) {
+            backward_layers<Spec, L - 1, FLAGS>(p, sW, adjIn, rowBase, n32, tile);
+        } else {
+            // adjoint of the encoded features -> shared tile, then one lane per point runs the encoding adjoints
+            constexpr int TS = SL::tileStride();
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+#pragma unroll
+                for (int j = 0; j < NC; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int rr = m * 16 + r + (e & 1) * 8;
+                        const int cc = j * 16 + (e >> 1) * 8 + q * 2;
+                        *reinterpret_cast<uint32_t*>(tile + rr * TS + cc) = adjIn[m][j][e];
+                    }
+            __syncwarp();
+            const long long myRow = rowBase + lane;
+            if (myRow < p.numel) {
+                RowReader in{p.input + myRow * p.inS0, p.inS1};
+                float* adjInRow = (FLAGS & FLAG_GRAD_INPUT) ? p.adjInput + myRow * p.aiS0 : nullptr;
+                encode_adjoint_point<Spec, 0, (FLAGS & FLAG_GRAD_INPUT) != 0, (FLAGS & FLAG_GRAD_ENCODINGS) != 0>(
+                    p, in, HalfRowReader{tile + lane * TS}, adjInRow, p.aiS1);
+            }
+            __syncwarp();
+        }
+    }
+}
+
+template <class Spec, int FLAGS>
+__global__ void __launch_bounds__(Spec::WARPS * 32, Spec::MIN_BLOCKS)
+fused_backward_kernel(const __grid_constant__ LaunchArgs p)
+{
+    using SL = SmemLayout<Spec>;
+    extern __shared__ __align__(16) unsigned char smem[];
+    __half* sW = reinterpret_cast<__half*>(smem);
+    float* sB = reinterpret_cast<float*>(smem + SL::biasStartBytes());
+    stage_layer<Spec, 0>(p, sW, sB);
+    __syncthreads();
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = lane >> 2, q = lane & 3;
+    __half* tile = reinterpret_cast<__half*>(smem + SL::tileStartBytes() + warp * SL::tileBytesPerWarp());
+    constexpr int LL = Spec::NUM_LAYERS - 1;
+    constexpr int KT = Spec::COUT[LL] / 16;
+    const long long n32 = (p.numel + 31) / 32 * 32;
+    const long long numTiles = n32 / TILE_POINTS;
+
+    for (long long t = static_cast<long long>(blockIdx.x) * Spec::WARPS + warp; t < numTiles;
+         t += static_cast<long long>(gridDim.x) * Spec::WARPS) {
+        const long long rowBase = t * TILE_POINTS;
+        // dL/dout (fp32, N x NUM_OUTPUTS) -> half fragments, zero padded (kernels/network_backward.cuh:67-80)
+        uint32_t adj[MT][KT][4];
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+#pragma unroll
+            for (int k = 0; k < KT; ++k)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const long long row = rowBase + m * 16 + r + (e & 1) * 8;
+                    const int col = k * 16 + (e >> 1) * 8 + q * 2;
+                    float v0 = 0.f, v1 = 0.f;
+                    if (row < p.numel) {
+                        if (col < Spec::NUM_OUTPUTS) v0 = __ldg(p.adjOutput + row * p.aoS0 + col * p.aoS1);
+                        if (col + 1 < Spec::NUM_OUTPUTS) v1 = __ldg(p.adjOutput + row * p.aoS0 + (col + 1) * p.aoS1);
+                    }
+                    adj[m][k][e] = h2_as_u32(__floats2half2_rn(v0, v1));
+                }
+        backward_layers<Spec, LL, FLAGS>(p, sW, adj, rowBase, n32, tile);
+    }
+}
+
+// ---- weight / bias gradient: split-batch tensor-core GEMM -------------------------------------------------------
+// dW_l (COUT x CIN) += sum_n delta_l[n,:]^T * a_{l-1}[n,:],  db_l += sum_n delta_l[n,:]
+// (math of tests_cpp/test_against_eigen2.cpp:187-200; replaces the single-block WeightUpdateSingleBlockKernel,
+// src_cpp/include/qmlp/kernels/network_weight_update_block.cuh:356-494). a_{l-1} is recomputed from the stashed
+// pre-activation (or is the stashed encoded input for l == 0). blockIdx.y selects the layer, blockIdx.x strides
+// over 64-point slabs; partial sums are added to the fp32 gradient vector with red.global.add.
+constexpr int WG_SLAB = 64;
+constexpr int WG_WARPS = 8;
+
+template <class Spec>
+struct WgradSmem {
+    __host__ __device__ static constexpr int maxCout() { int m = 0; for (int i = 0; i < Spec::NUM_LAYERS; ++i) m = Spec::COUT[i] > m ? Spec::COUT[i] : m; return m; }
+    __host__ __device__ static constexpr int maxCin() { int m = 0; for (int i = 0; i < Spec::NUM_LAYERS; ++i) m = Spec::CIN[i] > m ? Spec::CIN[i] : m; return m; }
+    __host__ __device__ static constexpr int bytes() { return 2 * WG_SLAB * ((maxCout() + 8) + (maxCin() + 8)) * 2; }
+};
+
+template <class Spec, int L>
+__device__ __forceinline__ void wgrad_layer(const LaunchArgs& p, unsigned char* smem)
+{
+    using SL = SmemLayout<Spec>;
+    constexpr int CIN = Spec::CIN[L], COUT = Spec::COUT[L];
+    constexpr int DS = COUT + 8, BS = CIN + 8;          // smem row strides (halfs)
+    constexpr int NBLK = (COUT / 16) * (CIN / 16);      // 16x16 output blocks
+    constexpr int WB = NBLK >= 8 ? 8 : NBLK >= 4 ? 4 : NBLK >= 2 ? 2 : 1; // warps across blocks
+    constexpr int KW = WG_WARPS / WB;                   // warps across the k16 steps of a slab
+    constexpr int PB = (NBLK + WB - 1) / WB;            // blocks per warp
+    constexpr int KSTEPS = WG_SLAB / 16;
+    constexpr bool BIAS = Spec::BOFF[L] >= 0;
+
+    __half* const sDbase = reinterpret_cast<__half*>(smem);            // [2][WG_SLAB][DS]
+    __half* const sAbase = sDbase + 2 * WG_SLAB * DS;                    // [2][WG_SLAB][BS]
+
+    const long long n32 = (p.numel + 31) / 32 * 32;
+    const __half* gD = p.adjTmp + n32 * SL::deltaOffset(L);
+    const __half* gA = L == 0 ? p.fwdTmp : p.fwdTmp + n32 * SL::preOffset(L > 0 ? L - 1 : 0);
+    const long long numSlabs = (p.numel + WG_SLAB - 1) / WG_SLAB;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wb = warp % WB, wk = warp / WB;
+
+    float acc[PB][2][4];
+    float accB[PB][4];
+#pragma unroll
+    for (int b = 0; b < PB; ++b) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { acc[b][0][e] = 0.f; acc[b][1][e] = 0.f; accB[b][e] = 0.f; }
+    }
+
+    auto load_slab = [&](long long slab, int buf) {
+        const long long row0 = slab * WG_SLAB;
+        constexpr int DCH = COUT / 8, ACH = CIN / 8;
+        for (int i = threadIdx.x; i < WG_SLAB * DCH; i += WG_WARPS * 32) {
+            const int rr = i / DCH, cc = i % DCH;
+            const bool ok = row0 + rr < p.numel;
+            cp_async16(smem_u32(sDbase + buf * WG_SLAB * DS + rr * DS + cc * 8), gD + (ok ? row0 + rr : 0) * COUT + cc * 8, ok);
+        }
+        for (int i = threadIdx.x; i < WG_SLAB * ACH; i += WG_WARPS * 32) {
+            const int rr = i / ACH, cc = i % ACH;
+            const bool ok = row0 + rr < p.numel;
+            cp_async16(smem_u32(sAbase + buf * WG_SLAB * BS + rr * BS + cc * 8), gA + (ok ? row0 + rr : 0) * CIN + cc * 8, ok);
+        }
+    };
+
+    long long slab = blockIdx.x;
+    int buf = 0;
+    if (slab < numSlabs) load_slab(slab, 0);
+    cp_async_commit();
+    for (; slab < numSlabs; slab += gridDim.x) {
+        const long long next = slab + gridDim.x;
+        if (next < numSlabs) load_slab(next, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const __half* d = sDbase + buf * WG_SLAB * DS;
+        const __half* a = sAbase + buf * WG_SLAB * BS;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            if (ks % KW != wk) continue;
+#pragma unroll
+            for (int b = 0; b < PB; ++b) {
+                const int blk = wb + b * WB;
+                if (blk >= NBLK) continue;
+                const int mb = blk / (CIN / 16), nb = blk % (CIN / 16);
+                // A fragment = delta^T (m = cout, k = point): transposing ldmatrix of the (point, cout) tile
+                uint32_t af[4], bf[4];
+                ldmatrix_x4_trans(af, smem_u32(d + (ks * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * DS + mb * 16 + ((lane >> 3) & 1) * 8));
+                // B fragment (k = point, n = cin): transposing ldmatrix of the (point, cin) tile
+                ldmatrix_x4_trans(bf, smem_u32(a + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * BS + nb * 16 + (lane >> 4) * 8));
+                if constexpr (L > 0) {
+                    using ActPrev = typename Spec::template Act<(L > 0 ? L - 1 : 0)>;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) bf[e] = h2_as_u32(ActPrev::forward2(u32_as_h2(bf[e])));
+                }
+                mma16816(acc[b][0], af, bf[0], bf[1]);
+                mma16816(acc[b][1], af, bf[2], bf[3]);
+                if constexpr (BIAS) {
+                    if (nb == 0) mma16816(accB[b], af, 0x3C003C00u, 0x3C003C00u); // B = ones: row sums of delta^T
+                }
+            }
+        }
+        __syncthreads();
+        buf ^= 1;
+    }
+    cp_async_wait<0>();
+
+    // partial sums -> fp32 gradient vector (accumulated, callers zero it: reference semantics "+=",
+    // kernels/network_weight_update_block.cuh:492)
+    const int r = lane >> 2, q = lane & 3;
+    float* gw = p.gradWeights + Spec::WOFF[L];
+#pragma unroll
+    for (int b = 0; b < PB; ++b) {
+        const int blk = wb + b * WB;
+        if (blk >= NBLK) continue;
+        const int mb = blk / (CIN / 16), nb = blk % (CIN / 16);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int m = mb * 16 + r + (e >> 1) * 8;
+                const int n = nb * 16 + h * 8 + q * 2 + (e & 1);
+                const float v = acc[b][h][e];
+                if (v != 0.f) red_add_f32(gw + m * CIN + n, v);
+            }
+        if constexpr (BIAS) {
+            if (nb == 0 && q == 0) {
+                float* gb = p.gradWeights + (BIAS ? Spec::BOFF[L] : 0);
+                if (accB[b][0] != 0.f) red_add_f32(gb + mb * 16 + r, accB[b][0]);
+                if (accB[b][2] != 0.f) red_add_f32(gb + mb * 16 + r + 8, accB[b][2]);
+            }
+        }
+    }
+}
+
+template <class Spec, int L>
+__device__ __forceinline__ void wgrad_dispatch(const LaunchArgs& p, unsigned char* smem)
+{
+    if constexpr (L < Spec::NUM_LAYERS) {
+        if (blockIdx.y == L) wgrad_layer<Spec, L>(p, smem);
+        else wgrad_dispatch<Spec, L + 1>(p, smem);
+    }
+}
+
+template <class Spec>
+__global__ void __launch_bounds__(WG_WARPS * 32, 2)
+wgrad_kernel(const __grid_constant__ LaunchArgs p)
+{
+    extern __shared__ __align__(16) unsigned char smem[];
+    wgrad_dispatch<Spec, 0>(p, smem);
+}
+
+// ---- host-side launchers (compiled into each instantiation) -------------------------------------------------------
+template <class Spec>
+struct NetworkLaunchers {
+    template <class K>
+    static cudaError_t setSmem(K kernel, int bytes)
+    {
+        return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    }
+
+    template <int MODE>
+    static cudaError_t forward(const LaunchArgs& a, cudaStream_t s)
+    {
+        constexpr int smem = SmemLayout<Spec>::totalBytes();
+        static bool configured = false;
+        auto k = fused_forward_kernel<Spec, MODE>;
+        if (!configured) {
+            cudaError_t e = setSmem(k, smem);
+            if (e != cudaSuccess) return e;
+            configured = true;
+        }
+        int perSM = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSM, k, Spec::WARPS * 32, smem);
+        if (e != cudaSuccess) return e;
+        if (perSM < 1) perSM = 1;
+        const long long tiles = (a.numel + TILE_POINTS - 1) / TILE_POINTS;
+        long long blocks = (tiles + Spec::WARPS - 1) / Spec::WARPS;
+        const long long cap = static_cast<long long>(a.numSMs) * perSM;
+        if (blocks > cap) blocks = cap;
+        if (blocks < 1) blocks = 1;
+        k<<<static_cast<unsigned>(blocks), Spec::WARPS * 32, smem, s>>>(a);
+        return cudaGetLastError();
+    }
+
+    template <int FLAGS>
+    static cudaError_t backwardT(const LaunchArgs& a, cudaStream_t s)
+    {
+        constexpr int smem = SmemLayout<Spec>::totalBytes();
+        static bool configured = false;
+        auto k = fused_backward_kernel<Spec, FLAGS>;
+        if (!configured) {
+            cudaError_t e = setSmem(k, smem);
+            if (e != cudaSuccess) return e;
+            configured = true;
+        }
+        int perSM = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSM, k, Spec::WARPS * 32, smem);
+        if (e != cudaSuccess) return e;
+        if (perSM < 1) perSM = 1;
+        const long long tiles = (a.numel + TILE_POINTS - 1) / TILE_POINTS;
+        long long blocks = (tiles + Spec::WARPS - 1) / Spec::WARPS;
+        const long long cap = static_cast<long long>(a.numSMs) * perSM;
+        if (blocks > cap) blocks = cap;
+        if (blocks < 1) blocks = 1;
+        k<<<static_cast<unsigned>(blocks), Spec::WARPS * 32, smem, s>>>(a);
+        return cudaGetLastError();
+    }
+
+    static cudaError_t backward(const LaunchArgs& a, cudaStream_t s)
+    {
+        switch (a.flags & 7) {
+        case 0: return cudaSuccess;
+        case 1: return backwardT<1>(a, s);
+        case 2: return backwardT<2>(a, s);
+        case 3: return backwardT<3>(a, s);
+        case 4: return backwardT<4>(a, s);
+        case 5: return backwardT<5>(a, s);
+        case 6: return backwardT<6>(a, s);
+        default: return backwardT<7>(a, s);
+        }
+    }
+
+    static cudaError_t wgrad(const LaunchArgs& a, cudaStream_t s)
+    {
+        constexpr int smem = WgradSmem<Spec>::bytes();
+        static bool configured = false;
+        auto k = wgrad_kernel<Spec>;
+        if (!configured) {
+            cudaError_t e = setSmem(k, smem);
+            if (e != cudaSuccess) return e;
+            configured = true;
+        }
+        const long long slabs = (a.numel + WG_SLAB - 1) / WG_SLAB;
+        long long gx = (static_cast<long long>(a.numSMs) * 2 + Spec::NUM_LAYERS - 1) / Spec::NUM_LAYERS;
+        if (gx > slabs) gx = slabs;
+        if (gx < 1) gx = 1;
+        dim3 grid(static_cast<unsigned>(gx), Spec::NUM_LAYERS);
+        k<<<grid, WG_WARPS * 32, smem, s>>>(a);
+        return cudaGetLastError();
+    }
+
+    static int launch(int kernel, const void* args, cudaStream_t s, int* launches)
+    {
+        const LaunchArgs& a = *static_cast<const LaunchArgs*>(args);
+        cudaError_t e = cudaErrorInvalidValue;
+        int n = 1;
+        switch (kernel) {
+        case KERNEL_INFERENCE: e = forward<0>(a, s); break;
+        case KERNEL_FORWARD: e = forward<1>(a, s); break;
+        case KERNEL_FORWARD_LOSS: e = forward<2>(a, s); break;
+        case KERNEL_BACKWARD: e = backward(a, s); n = (a.flags & 7) ? 1 : 0; break;
+        case KERNEL_WGRAD: e = wgrad(a, s); break;
+        default: break;
+        }
+        if (launches) *launches = (e == cudaSuccess) ? n : 0;
+        return static_cast<int>(e);
+    }
+};
+
+} // namespace kernel
+} // namespace qmlp

@@ -1,0 +1,88 @@
+// Plain structs shared by the host library and the per-spec kernel instantiations.
+// They replace the reference's __constant__ HashGridConfig marshalling
+// (src_cpp/include/qmlp/kernels/encoding_hashgrid_config.cuh:23-38, src_cpp/src/encoding_hashgrid.cpp:204-243):
+// the level table travels as a __grid_constant__ kernel parameter instead of a cuMemcpyHtoDAsync per launch.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace qmlp {
+namespace kernel {
+
+constexpr int MAX_GRID_LEVELS = 32;
+constexpr int MAX_GRIDS = 4;
+constexpr int MAX_GRID_DIMS = 6;
+
+struct GridLevelP {
+    unsigned int offset;       // element offset of the level inside the table (memoryOffset)
+    int resolution;            // per-side resolution
+    unsigned int hashGridSize; // rows if hashed (a power of two)
+    int hashed;                // 1: hashed lookup, 0: dense lookup
+};
+
+struct GridP {
+    const void* table; // fp32 (reference layout) or fp16 copy: [level0 rows*F | level1 ...]
+    float* grad;       // fp32 gradient table, same layout (may be null)
+    float boxMin[MAX_GRID_DIMS];
+    float boxInvSize[MAX_GRID_DIMS];
+    int tableIsHalf;
+    int vecOk; // table and grad pointers are aligned for whole-row vector access
+    GridLevelP levels[MAX_GRID_LEVELS];
+};
+
+// bits of LaunchArgs::flags for the backward kernel (AdjointMode of the reference,
+// src_cpp/include/qmlp/fused_network.h:22-34)
+constexpr int FLAG_GRAD_INPUT = 1;
+constexpr int FLAG_GRAD_WEIGHTS = 2;
+constexpr int FLAG_GRAD_ENCODINGS = 4;
+
+struct LaunchArgs {
+    long long numel;
+    const float* input;     long long inS0, inS1;
+    float* output;          long long outS0, outS1;
+    const float* adjOutput; long long aoS0, aoS1;
+    float* adjInput;        long long aiS0, aiS1;
+    const float* target;    long long tS0, tS1;   // fused L2 loss (training step)
+    float lossScale;                               // 2 / (global points * channels)
+    float* lossSum;                                // += sum (out-target)^2, may be null
+    const __half* weights;                         // flat fp16 parameter vector
+    float* gradWeights;                            // flat fp32 gradient vector
+    __half* fwdTmp;                                // stash: encoded input + pre-activations per layer
+    __half* adjTmp;                                // adjoint stash: delta per layer
+    int flags;
+    int numSMs;
+    int numGrids;
+    GridP grids[MAX_GRIDS];
+};
+
+// kernels a network instantiation exports through qmlp_spec_launch
+enum KernelId {
+    KERNEL_INFERENCE = 0,
+    KERNEL_FORWARD = 1,       // forward with stash
+    KERNEL_FORWARD_LOSS = 2,  // forward with stash, writes dLoss/dOut of the L2 loss instead of the output
+    KERNEL_BACKWARD = 3,      // flags select the variant
+    KERNEL_WGRAD = 4,
+    KERNEL_ENCODING_FORWARD = 5,
+    KERNEL_ENCODING_ADJOINT = 6,
+    KERNEL_ACTIVATION_FORWARD = 7,
+    KERNEL_ACTIVATION_ADJOINT = 8
+};
+
+// arguments of the stand-alone activation kernels
+struct ActivationArgs {
+    long long rows, cols;
+    const __half* input;     long long inS0, inS1;
+    const __half* adjOutput; long long aoS0, aoS1;
+    __half* output;          long long outS0, outS1; // forward: z; adjoint: adjx
+};
+
+} // namespace kernel
+} // namespace qmlp
+
+// entry points every instantiation exports
+extern "C" {
+typedef int (*qmlp_spec_launch_fn)(int kernel, const void* args, cudaStream_t stream, int* launches);
+typedef int (*qmlp_spec_abi_fn)(void);
+}
+#define QMLP_SPEC_ABI_VERSION 3

@@ -1,0 +1,64 @@
+"""Instantiates kernel templates for a list of specs ahead of time, several nvcc processes at once.
+The library would build a missing instantiation on first use; doing it here keeps compile time out of the GPU run.
+
+Jobs are tuples ("net", cfg_json, grid_half_mask) | ("enc", cfg_json, half_table) | ("act", key_or_json, 0).
+"""
+import json
+import os
+import subprocess
+import sys
+import tempfile
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def run_jobs(jobs):
+    if HERE not in sys.path:
+        sys.path.insert(0, HERE)
+    from qmlp import bindings
+    bindings.QuickMLP.set_log_level("error")
+    errors = []
+    for job in jobs:
+        try:
+            kind = job[0]
+            if kind == "net":
+                bindings.Network(job[1]).compile(int(job[2]))
+            elif kind == "enc":
+                bindings.Encoding(job[1]).compile(bool(job[2]))
+            elif kind == "act":
+                bindings.Activation(job[1]).compile()
+            else:
+                raise ValueError(kind)
+        except Exception as e:
+            errors.append(f"{job[0]} {job[1][:120]}: {e}")
+    return errors
+
+
+def prebuild(jobs, processes=None):
+    jobs = [list(j) for j in dict.fromkeys(tuple(j) for j in jobs)]
+    if not jobs:
+        return
+    processes = max(1, min(len(jobs), processes or os.cpu_count() or 4))
+    with tempfile.TemporaryDirectory() as tmp:
+        procs = []
+        for i in range(processes):
+            path = os.path.join(tmp, f"jobs{i}.json")
+            with open(path, "w") as f:
+                json.dump(jobs[i::processes], f)
+            procs.append(subprocess.Popen([sys.executable, os.path.abspath(__file__), path],
+                                          stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+        failed = []
+        for p in procs:
+            out, _ = p.communicate()
+            if p.returncode != 0:
+                failed.append(out[-4000:])
+    if failed:
+        raise RuntimeError("kernel instantiation failed:\n" + "\n".join(failed))
+
+
+if __name__ == "__main__":
+    with open(sys.argv[1]) as f:
+        errs = run_jobs(json.load(f))
+    if errs:
+        print("\n".join(errs))
+        sys.exit(1)

@@ -1,0 +1,149 @@
+"""Fused training step and batch sharding for one process per GPU.
+
+The reference has no trainer: its users write ``mse_loss`` + ``torch.optim.Adam`` around ``FusedNetwork.forward``
+(tests_py/qmlp_tests/test_network_image.py:41-55). ``FusedTrainer`` runs that loop as four kernels per step
+(forward with stash and loss gradient, backward with grid scatter, weight/bias gradients, Adam) over one fused
+fp32 gradient buffer ``[network | encoding 0 | encoding 1 ...]``. With ``torch.distributed`` initialised the buffer
+is all-reduced once per step (data parallel); inference needs no communication and is sharded by ``shard_points``.
+"""
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _capi
+from ._capi import check, current_stream, lib, wrap
+from .bindings import Network
+
+
+def shard_points(num_points: int, rank: int, world_size: int):
+    """Contiguous, balanced shard [begin, end) of a point batch for ``rank``; the first ``num_points % world_size``
+    ranks hold one point more."""
+    base, rem = divmod(num_points, world_size)
+    begin = rank * base + min(rank, rem)
+    return begin, begin + base + (1 if rank < rem else 0)
+
+
+class _CudaStep:
+    """The compute backend of a training step: the CUDA kernels behind the C ABI."""
+
+    def __init__(self, network: Network, lr, beta1, beta2, eps, grid_half_copy, device):
+        self.network = network
+        cfg = _capi.TrainerConfig(lr, beta1, beta2, eps, int(grid_half_copy), 0)
+        h = C.c_void_p()
+        check(lib().qmlp_trainer_create(network._h, C.byref(cfg), C.byref(h)))
+        self._h = h
+        self.fused_count = lib().qmlp_trainer_fused_count(h)
+        self.segments = [lib().qmlp_trainer_segment_start(h, i) for i in range(1 + network.num_encodings())]
+        self.device = device
+        self._workspace = None
+
+    def __del__(self):
+        if getattr(self, "_h", None) and _capi._lib is not None:
+            _capi._lib.qmlp_trainer_destroy(self._h)
+            self._h = None
+
+    def bind(self, master, grad, m, v, half):
+        check(lib().qmlp_trainer_bind(self._h, master.data_ptr(), grad.data_ptr(), m.data_ptr(), v.data_ptr(), half.data_ptr()))
+
+    def refresh_half(self):
+        check(lib().qmlp_trainer_refresh_half(self._h, current_stream()))
+
+    def gradients(self, x, target, global_points, loss_sum):
+        b = C.c_size_t()
+        check(lib().qmlp_trainer_workspace_bytes(self._h, x.shape[0], C.byref(b)))
+        if self._workspace is None or self._workspace.numel() < b.value:
+            self._workspace = torch.empty((b.value,), dtype=torch.uint8, device=x.device)
+        check(lib().qmlp_trainer_gradients(self._h, wrap(x), wrap(target), global_points, self._workspace.data_ptr(),
+                                           self._workspace.numel(), loss_sum.data_ptr() if loss_sum is not None else None,
+                                           current_stream()))
+
+    def update(self, step, grad_scale):
+        check(lib().qmlp_trainer_update(self._h, step, grad_scale, current_stream()))
+
+
+class FusedTrainer:
+    """Data-parallel fused trainer for one replica of a network.
+
+    master / gradient / Adam moments are fp32 vectors of ``fused_count`` elements; ``half`` is the fp16 working copy
+    the kernels read (network weights always, grid tables when ``grid_half_copy``). Gradients are normalised by the
+    global point count inside the kernels, so the all-reduce is a plain sum.
+    """
+
+    def __init__(self, network: Network, lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-8, grid_half_copy=True,
+                 device="cuda", process_group=None, backend=None):
+        self.network = network
+        self.device = torch.device(device)
+        self.backend = backend if backend is not None else _CudaStep(network, lr, beta1, beta2, eps, grid_half_copy, self.device)
+        n = self.backend.fused_count
+        self.master = torch.zeros((n,), dtype=torch.float32, device=self.device)
+        self.gradient = torch.zeros((n,), dtype=torch.float32, device=self.device)
+        self.adam_m = torch.zeros((n,), dtype=torch.float32, device=self.device)
+        self.adam_v = torch.zeros((n,), dtype=torch.float32, device=self.device)
+        self.half = torch.zeros((n,), dtype=torch.float16, device=self.device)
+        self.loss_sum = torch.zeros((1,), dtype=torch.float32, device=self.device)
+        self.backend.bind(self.master, self.gradient, self.adam_m, self.adam_v, self.half)
+        self.step_count = 0
+        self.process_group = process_group
+
+    # -- parameter access ---------------------------------------------------------------------------------------------
+    def segment(self, buffer: torch.Tensor, index: int) -> Optional[torch.Tensor]:
+        """View of segment ``index`` (0 = network, 1 + i = encoding i) of one of the fused buffers."""
+        start = self.backend.segments[index]
+        if start < 0:
+            return None
+        count = self.network.num_network_parameters() if index == 0 else self.network.encoding(index - 1).parameter_count()
+        return buffer[start:start + count]
+
+    def set_parameters(self, network_parameters: torch.Tensor, encoding_parameters=()):
+        """Loads fp32 (or fp16) parameters into the master copy and refreshes the half copy."""
+        self.segment(self.master, 0).copy_(network_parameters.to(torch.float32))
+        for i, p in enumerate(encoding_parameters):
+            if p is not None and self.backend.segments[1 + i] >= 0:
+                self.segment(self.master, 1 + i).copy_(p.to(torch.float32))
+        self.backend.refresh_half()
+
+    def state_dict(self):
+        return {"master": self.master, "adam_m": self.adam_m, "adam_v": self.adam_v, "step": self.step_count}
+
+    def load_state_dict(self, state):
+        self.master.copy_(state["master"])
+        self.adam_m.copy_(state["adam_m"])
+        self.adam_v.copy_(state["adam_v"])
+        self.step_count = int(state["step"])
+        self.backend.refresh_half()
+
+    # -- one step -----------------------------------------------------------------------------------------------------
+    def _world(self):
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized():
+            return dist, dist.get_world_size(self.process_group)
+        return None, 1
+
+    def step(self, x: torch.Tensor, target: torch.Tensor, global_points: Optional[int] = None):
+        """forward + L2 loss + backward + (all-reduce) + Adam on this rank's points.
+        ``global_points`` defaults to ``world_size * x.shape[0]`` (equal shards)."""
+        dist, world = self._world()
+        if global_points is None:
+            global_points = world * x.shape[0]
+        self.backend.gradients(x, target, global_points, self.loss_sum)
+        if world > 1:
+            dist.all_reduce(self.gradient, op=dist.ReduceOp.SUM, group=self.process_group)
+        self.step_count += 1
+        self.backend.update(self.step_count, 1.0)
+
+    def mean_loss(self, global_points: int, reset=True) -> float:
+        """Mean squared error accumulated since the last reset (synchronises)."""
+        dist, world = self._world()
+        s = self.loss_sum.clone()
+        if world > 1:
+            dist.all_reduce(s, op=dist.ReduceOp.SUM, group=self.process_group)
+        if reset:
+            self.loss_sum.zero_()
+        return float(s.item()) / (global_points * self.network.channels_out())
+
+    def inference(self, x: torch.Tensor) -> torch.Tensor:
+        """Fused inference with the current half copy of all parameters."""
+        out = torch.empty((x.shape[0], self.network.channels_out()), dtype=torch.float32, device=x.device)
+        check(lib().qmlp_network_inference(self.network._h, wrap(x), wrap(out), current_stream()))
+        return out
