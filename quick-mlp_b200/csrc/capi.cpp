@@ -41,7 +41,10 @@ void checkLaunch(int e, const char* what)
 
 void checkDefined(const qmlp_tensor_t* t, const char* name)
 {
-    if (t == nullptr || t->ndim <= 0 || t->data == nullptr) throw std::runtime_error(std::string(name) + " is undefined");
+    if (t == nullptr || t->ndim <= 0) throw std::runtime_error(std::string(name) + " is undefined");
+    bool empty = false;
+    for (int i = 0; i < t->ndim && i < 2; ++i) empty = empty || t->sizes[i] == 0;
+    if (t->data == nullptr && !empty) throw std::runtime_error(std::string(name) + " is undefined");
 }
 void checkDim(const qmlp_tensor_t* t, int dim, const char* name)
 {

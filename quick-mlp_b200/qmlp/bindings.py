@@ -52,9 +52,12 @@ class Activation:
         self._h = h
 
     def __del__(self):
-        if getattr(self, "_h", None) and _capi._lib is not None:
-            _capi._lib.qmlp_activation_destroy(self._h)
-            self._h = None
+        try:
+            if getattr(self, "_h", None) and _capi._lib is not None:
+                _capi._lib.qmlp_activation_destroy(self._h)
+                self._h = None
+        except Exception:   # interpreter shutdown: module globals may already be gone
+            pass
 
     def cfg(self) -> str:
         return self._cfg
@@ -114,9 +117,12 @@ class Encoding:
         self._cfg = self.to_json()
 
     def __del__(self):
-        if getattr(self, "_owned", False) and getattr(self, "_h", None) and _capi._lib is not None:
-            _capi._lib.qmlp_encoding_destroy(self._h)
-            self._h = None
+        try:
+            if getattr(self, "_owned", False) and getattr(self, "_h", None) and _capi._lib is not None:
+                _capi._lib.qmlp_encoding_destroy(self._h)
+                self._h = None
+        except Exception:   # interpreter shutdown: module globals may already be gone
+            pass
 
     def cfg(self) -> str:
         return self._cfg
@@ -235,9 +241,12 @@ class Network:
         self._mutex = threading.Lock()   # parameter pointers are instance state, bind_network.h:20
 
     def __del__(self):
-        if getattr(self, "_h", None) and _capi._lib is not None:
-            _capi._lib.qmlp_network_destroy(self._h)
-            self._h = None
+        try:
+            if getattr(self, "_h", None) and _capi._lib is not None:
+                _capi._lib.qmlp_network_destroy(self._h)
+                self._h = None
+        except Exception:   # interpreter shutdown: module globals may already be gone
+            pass
 
     def cfg(self) -> str:
         return self._cfg

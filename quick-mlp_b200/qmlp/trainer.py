@@ -39,9 +39,12 @@ class _CudaStep:
         self._workspace = None
 
     def __del__(self):
-        if getattr(self, "_h", None) and _capi._lib is not None:
-            _capi._lib.qmlp_trainer_destroy(self._h)
-            self._h = None
+        try:
+            if getattr(self, "_h", None) and _capi._lib is not None:
+                _capi._lib.qmlp_trainer_destroy(self._h)
+                self._h = None
+        except Exception:   # interpreter shutdown: module globals may already be gone
+            pass
 
     def bind(self, master, grad, m, v, half):
         check(lib().qmlp_trainer_bind(self._h, master.data_ptr(), grad.data_ptr(), m.data_ptr(), v.data_ptr(), half.data_ptr()))
