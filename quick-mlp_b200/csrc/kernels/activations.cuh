@@ -42,7 +42,8 @@ __device__ __forceinline__ __half2 select_gt0(__half2 x, __half2 ifTrue, __half2
 
 // "z = __hgt(x, hZERO()) ? x : hZERO()" / "adjx = __hgt(x, hZERO()) ? adjz : hZERO()"
 struct BuiltinRelu {
-    static __device__ __forceinline__ __half2 forward2(__half2 x) { return select_gt0(x, x, __float2half2_rn(0.f)); }
+    // max(x, 0) returns the non-NaN operand, i.e. 0 for NaN, like the comparison form
+    static __device__ __forceinline__ __half2 forward2(__half2 x) { return __hmax2(x, __float2half2_rn(0.f)); }
     static __device__ __forceinline__ __half2 adjoint2(__half2 x, __half2 adjz) { return select_gt0(x, adjz, __float2half2_rn(0.f)); }
     static __device__ __forceinline__ half forward(half x) { return __hgt(x, hZERO()) ? x : hZERO(); }
     static __device__ __forceinline__ half adjoint(half x, half adjz) { return __hgt(x, hZERO()) ? adjz : hZERO(); }
@@ -50,13 +51,19 @@ struct BuiltinRelu {
 
 // "z = __hgt(x, hZERO()) ? x : __hsub(hexp(x), 1)" / "adjx = __hgt(x, hZERO()) ? adjz : __hmul(adjz, hexp(x))"
 struct BuiltinCelu {
+    // exp(x) = 2^(x * log2 e) on the half2 special-function path; only used for x <= 0, where the fp16 rounding of
+    // the product costs less than one fp16 ulp of the result
+    static __device__ __forceinline__ __half2 fast_exp2(__half2 x)
+    {
+        return h2exp2(__hmul2(x, __float2half2_rn(1.4426950408889634f)));
+    }
     static __device__ __forceinline__ __half2 forward2(__half2 x)
     {
-        return select_gt0(x, x, __hsub2(h2exp(x), __float2half2_rn(1.0f)));
+        return select_gt0(x, x, __hsub2(fast_exp2(x), __float2half2_rn(1.0f)));
     }
     static __device__ __forceinline__ __half2 adjoint2(__half2 x, __half2 adjz)
     {
-        return select_gt0(x, adjz, __hmul2(adjz, h2exp(x)));
+        return select_gt0(x, adjz, __hmul2(adjz, fast_exp2(x)));
     }
     static __device__ __forceinline__ half forward(half x) { return __hgt(x, hZERO()) ? x : __hsub(hexp(x), __float2half(1.0f)); }
     static __device__ __forceinline__ half adjoint(half x, half adjz) { return __hgt(x, hZERO()) ? adjz : __hmul(adjz, hexp(x)); }
@@ -64,8 +71,18 @@ struct BuiltinCelu {
 
 // "z = hsin(x)" / "adjx = __hmul(hcos(x), adjz)"
 struct BuiltinSine {
-    static __device__ __forceinline__ __half2 forward2(__half2 x) { return h2sin(x); }
-    static __device__ __forceinline__ __half2 adjoint2(__half2 x, __half2 adjz) { return __hmul2(h2cos(x), adjz); }
+    // fp32 special-function unit (sin.approx / cos.approx, absolute error ~1e-6 for the |x| an fp16 pre-activation can
+    // hold with useful precision), rounded once to half
+    static __device__ __forceinline__ __half2 forward2(__half2 x)
+    {
+        const float2 f = __half22float2(x);
+        return __floats2half2_rn(__sinf(f.x), __sinf(f.y));
+    }
+    static __device__ __forceinline__ __half2 adjoint2(__half2 x, __half2 adjz)
+    {
+        const float2 f = __half22float2(x);
+        return __hmul2(__floats2half2_rn(__cosf(f.x), __cosf(f.y)), adjz);
+    }
     static __device__ __forceinline__ half forward(half x) { return hsin(x); }
     static __device__ __forceinline__ half adjoint(half x, half adjz) { return __hmul(hcos(x), adjz); }
 };

@@ -42,7 +42,7 @@ struct EncGrid {
 };
 
 // ---- shared memory layout ------------------------------------------------------------------------------------
-// weights of layer l: [COUT][CIN + 8] halfs (row padded by 16 bytes: conflict-free ldmatrix), then fp32 biases,
+// weights of layer l: [COUT][CIN + 8] halfs (row padded by 16 bytes: conflict-free ldmatrix), then the biases (half),
 // then one [32][CIN0 + 8] half tile per warp.
 template <class Spec>
 struct SmemLayout {
@@ -55,16 +55,16 @@ struct SmemLayout {
         return o;
     }
     __host__ __device__ static constexpr int weightHalfs() { return wOffsetHalfs(NL); }
-    __host__ __device__ static constexpr int biasOffsetFloats(int l)
+    __host__ __device__ static constexpr int biasOffset(int l)
     {
         int o = 0;
         for (int i = 0; i < l; ++i) o += Spec::COUT[i];
         return o;
     }
-    __host__ __device__ static constexpr int biasFloats() { return biasOffsetFloats(NL); }
+    __host__ __device__ static constexpr int biasHalfs() { return biasOffset(NL); }
     __host__ __device__ static constexpr int biasStartBytes() { return ((weightHalfs() * 2 + 15) / 16) * 16; }
     __host__ __device__ static constexpr int tileStride() { return Spec::CIN[0] + 8; }
-    __host__ __device__ static constexpr int tileStartBytes() { return ((biasStartBytes() + biasFloats() * 4 + 15) / 16) * 16; }
+    __host__ __device__ static constexpr int tileStartBytes() { return ((biasStartBytes() + biasHalfs() * 2 + 15) / 16) * 16; }
     __host__ __device__ static constexpr int tileBytesPerWarp() { return TILE_POINTS * tileStride() * 2; }
     __host__ __device__ static constexpr int totalBytes() { return tileStartBytes() + Spec::WARPS * tileBytesPerWarp(); }
     // prefix sums of the stash (in halfs per point)
@@ -83,7 +83,7 @@ struct SmemLayout {
 };
 
 template <class Spec, int L>
-__device__ __forceinline__ void stage_layer(const LaunchArgs& p, __half* sW, float* sB)
+__device__ __forceinline__ void stage_layer(const LaunchArgs& p, __half* sW, __half* sB)
 {
     if constexpr (L < Spec::NUM_LAYERS) {
         using SL = SmemLayout<Spec>;
@@ -96,9 +96,9 @@ __device__ __forceinline__ void stage_layer(const LaunchArgs& p, __half* sW, flo
             const uint4 v = *reinterpret_cast<const uint4*>(gW + r * CIN + c * 8);
             *reinterpret_cast<uint4*>(dW + r * SL::wStride(L) + c * 8) = v;
         }
-        float* dB = sB + SL::biasOffsetFloats(L);
+        __half* dB = sB + SL::biasOffset(L);
         for (int i = threadIdx.x; i < COUT; i += blockDim.x)
-            dB[i] = Spec::BOFF[L] >= 0 ? __half2float(p.weights[(Spec::BOFF[L] >= 0 ? Spec::BOFF[L] : 0) + i]) : 0.f;
+            dB[i] = Spec::BOFF[L] >= 0 ? p.weights[(Spec::BOFF[L] >= 0 ? Spec::BOFF[L] : 0) + i] : __ushort_as_half(0);
         stage_layer<Spec, L + 1>(p, sW, sB);
     }
 }
@@ -162,7 +162,7 @@ __device__ __forceinline__ void encode_point(const LaunchArgs& p, const RowReade
 // ---- forward layer chain -------------------------------------------------------------------------------------
 // MODE 0: inference, 1: forward with stash, 2: forward with stash + L2 loss gradient instead of the output
 template <class Spec, int L, int MODE>
-__device__ __forceinline__ void forward_layers(const LaunchArgs& p, const __half* sW, const float* sB,
+__device__ __forceinline__ void forward_layers(const LaunchArgs& p, const __half* sW, const __half* sB,
                                                uint32_t (&aIn)[MT][Spec::CIN[L] / 16][4], long long rowBase, long long n32,
                                                float& lossAcc)
 {
@@ -175,7 +175,8 @@ __device__ __forceinline__ void forward_layers(const LaunchArgs& p, const __half
     const int lane = threadIdx.x & 31;
     const int r = lane >> 2, q = lane & 3;
     const __half* w = sW + SL::wOffsetHalfs(L);
-    const float* bias = sB + SL::biasOffsetFloats(L);
+    const __half* bias = sB + SL::biasOffset(L);
+    constexpr bool BIAS = Spec::BOFF[L] >= 0;
     // ldmatrix lane address of the B fragments: two n8 tiles x (k 0-7, k 8-15)
     const uint32_t wAddr = smem_u32(w + ((lane & 7) + ((lane >> 4) << 3)) * WS + ((lane >> 3) & 1) * 8);
 
@@ -187,11 +188,11 @@ __device__ __forceinline__ void forward_layers(const LaunchArgs& p, const __half
         }
         float acc[MT][2][4];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const float b0 = bias[j * 16 + h * 8 + q * 2], b1 = bias[j * 16 + h * 8 + q * 2 + 1];
+        for (int m = 0; m < MT; ++m)
 #pragma unroll
-            for (int m = 0; m < MT; ++m) { acc[m][h][0] = b0; acc[m][h][1] = b1; acc[m][h][2] = b0; acc[m][h][3] = b1; }
-        }
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[m][h][e] = 0.f;
 #pragma unroll
         for (int k = 0; k < KT; ++k) {
             uint32_t b[4];
@@ -206,10 +207,16 @@ __device__ __forceinline__ void forward_layers(const LaunchArgs& p, const __half
         for (int m = 0; m < MT; ++m) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const __half2 lo = __floats2half2_rn(acc[m][h][0], acc[m][h][1]); // row r
-                const __half2 hi = __floats2half2_rn(acc[m][h][2], acc[m][h][3]); // row r + 8
-                const long long row0 = rowBase + m * 16 + r;
                 const int col = j * 16 + h * 8 + q * 2;
+                __half2 lo = __floats2half2_rn(acc[m][h][0], acc[m][h][1]); // row r
+                __half2 hi = __floats2half2_rn(acc[m][h][2], acc[m][h][3]); // row r + 8
+                if constexpr (BIAS) {
+                    // the fp32 accumulator is rounded to half first, then the (half) bias is added
+                    const __half2 b2 = *reinterpret_cast<const __half2*>(bias + col);
+                    lo = __hadd2(lo, b2);
+                    hi = __hadd2(hi, b2);
+                }
+                const long long row0 = rowBase + m * 16 + r;
                 if constexpr (MODE >= 1) {
                     // pre-activation stash, row-major (N32, COUT) per layer (reference: kernels/layer.cuh:156-163)
                     __half* st = p.fwdTmp + n32 * SL::preOffset(L);
@@ -252,7 +259,7 @@ fused_forward_kernel(const __grid_constant__ LaunchArgs p)
     using SL = SmemLayout<Spec>;
     extern __shared__ __align__(16) unsigned char smem[];
     __half* sW = reinterpret_cast<__half*>(smem);
-    float* sB = reinterpret_cast<float*>(smem + SL::biasStartBytes());
+    __half* sB = reinterpret_cast<__half*>(smem + SL::biasStartBytes());
     stage_layer<Spec, 0>(p, sW, sB);
     __syncthreads();
 
@@ -449,7 +456,7 @@ fused_backward_kernel(const __grid_constant__ LaunchArgs p)
     using SL = SmemLayout<Spec>;
     extern __shared__ __align__(16) unsigned char smem[];
     __half* sW = reinterpret_cast<__half*>(smem);
-    float* sB = reinterpret_cast<float*>(smem + SL::biasStartBytes());
+    __half* sB = reinterpret_cast<__half*>(smem + SL::biasStartBytes());
     stage_layer<Spec, 0>(p, sW, sB);
     __syncthreads();
 
