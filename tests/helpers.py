@@ -73,3 +73,20 @@ def grid_tables(spec: "oracle.NetSpec", seed=13, scale=1.0):
     for i, e in enumerate(spec.encodings):
         out.append(uniform(seed, 500 + i, (e.num_parameters,), -scale, scale) if e.num_parameters else None)
     return out
+
+
+def pack_parameters(spec: "oracle.NetSpec", weights, biases):
+    """Unpadded per-layer (n_out, n_in) weights / (n_out,) biases -> the padded flat fp32 vector (padding zero)."""
+    p = np.zeros(spec.num_parameters, dtype=np.float32)
+    for i, l in enumerate(spec.layers):
+        w = np.zeros((l.channels_out, l.channels_in), dtype=np.float32)
+        w[:weights[i].shape[0], :weights[i].shape[1]] = weights[i]
+        p[l.weights_start:l.weights_start + w.size] = w.ravel()
+        if l.use_bias and biases[i] is not None:
+            p[l.bias_start:l.bias_start + biases[i].shape[0]] = biases[i]
+    return p
+
+
+def load_golden(name):
+    import os
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", name))
