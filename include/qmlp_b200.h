@@ -80,6 +80,15 @@ QMLP_API const char* qmlp_get_kernel_cache_dir(void);
 /* Directory holding the kernel template headers used to instantiate a spec. */
 QMLP_API int qmlp_set_kernel_include_dir(const char* dir);
 
+/* Kernel family used for fused inference: 0 = the best one instantiated for the spec (tcgen05 tensor-core kernel when
+ * the layer widths allow it), 1 = the mma.sync kernels only. Takes the place of the reference's per-kernel tuning
+ * options (overwrite_blocksize_*, skew_shared_memory; src_cpp/src/fused_network.cpp:45-69). */
+QMLP_API int qmlp_set_kernel_path(int path);
+/* Synchronises the current device and returns (then clears) its kernel status word: 0 = every kernel ran to completion,
+ * 1 = a kernel gave up on a bounded on-chip wait and its results are invalid. The reference has no counterpart (its
+ * kernels contain no waits); debugging aids there are printf paths (src_cpp/include/qmlp/kernels/layer.cuh:28-41). */
+QMLP_API int qmlp_device_status(int* status);
+
 /* ---- FusedNetwork: src_cpp/include/qmlp/fused_network.h:16-340 ------------------------------- */
 /* FusedNetwork::FusedNetwork(cfg, parent), src_cpp/src/fused_network.cpp:33-223. cfg is the JSON text. */
 QMLP_API int qmlp_network_create(const char* cfg_json, const char* parent_dir, qmlp_network_t** out);

@@ -77,6 +77,8 @@ void fillCommon(Network& n, kernel::LaunchArgs& a, const qmlp_tensor_t* input)
     a.weights = static_cast<const __half*>(n.paramInference.data);
     a.gradWeights = static_cast<float*>(n.paramGradients.data);
     a.numSMs = Library::instance().smCount();
+    a.forcePath = Library::instance().kernelPath;
+    a.status = Library::instance().statusWord();
     n.fillGrids(a);
     for (int i = 0; i < n.numEncodings(); ++i) {
         auto e = n.encoding(i);
@@ -143,6 +145,25 @@ const char* qmlp_get_kernel_cache_dir(void)
     return s.c_str();
 }
 int qmlp_set_kernel_include_dir(const char* dir) { Library::instance().includeDir = dir ? dir : ""; return QMLP_OK; }
+
+int qmlp_set_kernel_path(int path)
+{
+    QMLP_TRY
+    if (path != 0 && path != 1) throw std::runtime_error("kernel path must be 0 (best for the spec) or 1 (mma.sync only)");
+    Library::instance().kernelPath = path;
+    QMLP_CATCH
+}
+
+int qmlp_device_status(int* status)
+{
+    QMLP_TRY
+    if (!status) throw std::runtime_error("null argument");
+    int* w = Library::instance().statusWord();
+    checkCuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+    checkCuda(cudaMemcpy(status, w, sizeof(int), cudaMemcpyDeviceToHost), "cudaMemcpy");
+    if (*status != 0) checkCuda(cudaMemset(w, 0, sizeof(int)), "cudaMemset");
+    QMLP_CATCH
+}
 
 // ---- network -------------------------------------------------------------------------------------------------------
 int qmlp_network_create(const char* cfg_json, const char* parent_dir, qmlp_network_t** out)

@@ -43,6 +43,8 @@ struct Library {
     std::string resolveCacheDir();
     std::string resolveIncludeDir();
     int smCount(); // of the current device
+    int kernelPath = 0;    // 0: best kernels for the spec, 1: mma.sync kernels only
+    int* statusWord();     // device word of the current device that kernels set when a bounded wait gives up
 };
 
 // ---- per-spec kernel instantiation ------------------------------------------------------------------------------

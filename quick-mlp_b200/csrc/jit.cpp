@@ -94,6 +94,23 @@ int Library::smCount()
     return cached[dev];
 }
 
+int* Library::statusWord()
+{
+    static int* words[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) throw cuda_error("cudaGetDevice failed: no CUDA device available");
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (words[dev] == nullptr) {
+        // one 4-byte allocation per device for the life of the process, made at the first launch on that device
+        int* w = nullptr;
+        cudaError_t e = cudaMalloc(&w, sizeof(int));
+        if (e == cudaSuccess) e = cudaMemset(w, 0, sizeof(int));
+        if (e != cudaSuccess) throw cuda_error(std::string("status word allocation failed: ") + cudaGetErrorString(e));
+        words[dev] = w;
+    }
+    return words[dev];
+}
+
 static uint64_t fnv1a(const std::string& s, uint64_t h = 1469598103934665603ULL)
 {
     for (unsigned char c : s) { h ^= c; h *= 1099511628211ULL; }

@@ -642,6 +642,9 @@ wgrad_kernel(const __grid_constant__ LaunchArgs p)
 }
 
 // ---- host-side launchers (compiled into each instantiation) -------------------------------------------------------
+template <class Spec> struct TcLayout;     // fused_forward_tc.cuh
+template <class Spec> struct TcLaunchers;
+
 template <class Spec>
 struct NetworkLaunchers {
     template <class K>
@@ -737,7 +740,12 @@ struct NetworkLaunchers {
         cudaError_t e = cudaErrorInvalidValue;
         int n = 1;
         switch (kernel) {
-        case KERNEL_INFERENCE: e = forward<0>(a, s); break;
+        case KERNEL_INFERENCE:
+            if constexpr (TcLayout<Spec>::eligible()) {
+                if (a.forcePath != 1) { e = TcLaunchers<Spec>::inference(a, s); break; }
+            }
+            e = forward<0>(a, s);
+            break;
         case KERNEL_FORWARD: e = forward<1>(a, s); break;
         case KERNEL_FORWARD_LOSS: e = forward<2>(a, s); break;
         case KERNEL_BACKWARD: e = backward(a, s); n = (a.flags & 7) ? 1 : 0; break;

@@ -53,6 +53,8 @@ struct LaunchArgs {
     int flags;
     int numSMs;
     int numGrids;
+    int forcePath;                                 // 0: best path for the spec, 1: mma.sync kernels only
+    int* status;                                   // device word set to 1 when a kernel gave up on a bounded wait
     GridP grids[MAX_GRIDS];
 };
 
@@ -85,4 +87,4 @@ extern "C" {
 typedef int (*qmlp_spec_launch_fn)(int kernel, const void* args, cudaStream_t stream, int* launches);
 typedef int (*qmlp_spec_abi_fn)(void);
 }
-#define QMLP_SPEC_ABI_VERSION 3
+#define QMLP_SPEC_ABI_VERSION 4

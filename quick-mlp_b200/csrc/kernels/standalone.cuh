@@ -4,6 +4,7 @@
 // (src_cpp/include/qmlp/kernels/activation_kernels.cuh:28-62, launched by src_cpp/src/activation.cpp:64-150).
 #pragma once
 #include "fused_network.cuh"
+#include "fused_forward_tc.cuh"
 
 namespace qmlp {
 namespace kernel {

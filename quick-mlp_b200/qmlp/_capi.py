@@ -52,6 +52,8 @@ SIGNATURES = {
     "qmlp_set_kernel_cache_dir": (C.c_int, [C.c_char_p]),
     "qmlp_get_kernel_cache_dir": (C.c_char_p, []),
     "qmlp_set_kernel_include_dir": (C.c_int, [C.c_char_p]),
+    "qmlp_set_kernel_path": (C.c_int, [C.c_int]),
+    "qmlp_device_status": (C.c_int, [C.POINTER(C.c_int)]),
     "qmlp_network_create": (C.c_int, [C.c_char_p, C.c_char_p, C.POINTER(_P)]),
     "qmlp_network_destroy": (None, [_P]),
     "qmlp_network_channels_in": (C.c_int, [_P]),

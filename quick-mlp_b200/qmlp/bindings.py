@@ -42,6 +42,19 @@ class QuickMLP:
     def kernel_cache_dir() -> str:
         return lib().qmlp_get_kernel_cache_dir().decode()
 
+    @staticmethod
+    def set_kernel_path(path: int):
+        """0: best kernels instantiated for a spec (tcgen05 inference when the widths allow), 1: mma.sync only."""
+        check(lib().qmlp_set_kernel_path(int(path)))
+
+    @staticmethod
+    def device_status() -> int:
+        """Synchronises and returns (then clears) the device status word: non-zero means a kernel gave up on a
+        bounded wait and its outputs are invalid."""
+        s = C.c_int(0)
+        check(lib().qmlp_device_status(C.byref(s)))
+        return s.value
+
 
 # ---------------------------------------------------------------------------------------------------------------------
 class Activation:

@@ -25,3 +25,16 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _device_status_is_clean(request):
+    """After every GPU test: no kernel may have given up on a bounded on-chip wait."""
+    yield
+    if "gpu" not in request.keywords:
+        return
+    import torch
+    if not torch.cuda.is_available():
+        return
+    from qmlp import bindings
+    assert bindings.QuickMLP.device_status() == 0, "a kernel reported a timed-out wait"

@@ -91,6 +91,30 @@ def test_inference(name, n):
     helpers.assert_close(out, ref, f"{name} inference vs fp32 oracle", max_violations=helpers.MAX_VIOLATIONS)
 
 
+@pytest.mark.parametrize("name", ["config2", "uneven", "custom_act", "config4_small", "config5_small"])
+@pytest.mark.parametrize("n", [127, 128, 5000, 40001])
+def test_tensor_core_paths_agree(name, n):
+    """The tcgen05 inference kernel and the mma.sync kernel compute the same function (same rounding points: fp32
+    accumulate, one rounding to half per layer), and no kernel reports a timed-out on-chip wait."""
+    import torch
+    from qmlp import bindings
+    cfg, rng, spec, net, params, tables, acts, t_params, t_tables = _setup(name)
+    x = torch.from_numpy(helpers.uniform(42, 7, (n, spec.num_inputs), *rng)).cuda()
+    try:
+        bindings.QuickMLP.set_kernel_path(0)
+        out_best = net.inference(x, t_params, t_tables)
+        bindings.QuickMLP.set_kernel_path(1)
+        out_mma = net.inference(x, t_params, t_tables)
+    finally:
+        bindings.QuickMLP.set_kernel_path(0)
+    assert bindings.QuickMLP.device_status() == 0
+    emu = oracle.network_forward(spec, params, x.cpu().numpy(), tables, half=True, activations=acts)
+    helpers.assert_close(out_best.cpu().numpy(), emu, f"{name} best path vs oracle", max_violations=0.01)
+    # accumulation order differs (K in steps of 16 inside one instruction vs per-fragment), so allow a few half ulps
+    helpers.assert_close(out_best.cpu().numpy(), out_mma.cpu().numpy(), f"{name} tcgen05 vs mma.sync", rtol=5e-3, atol=1e-3,
+                         max_violations=0.005)
+
+
 def test_inference_half_tables_and_strided_io():
     """fp16 gather table (extension) and non-contiguous input/output views."""
     import torch
