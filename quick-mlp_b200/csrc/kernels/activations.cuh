@@ -28,6 +28,8 @@ struct ScalarActivation {
     }
     static __device__ __forceinline__ half forward(half x) { return A::forward(x); }
     static __device__ __forceinline__ half adjoint(half x, half adjz) { return A::adjoint(x, adjz); }
+    // activation of two fp32 pre-activations, result as half2: round to half, then the half snippet
+    static __device__ __forceinline__ __half2 forward_f32x2(float a, float b) { return forward2(__floats2half2_rn(a, b)); }
 };
 
 __device__ __forceinline__ __half2 select_gt0(__half2 x, __half2 ifTrue, __half2 ifFalse)
@@ -47,6 +49,13 @@ struct BuiltinRelu {
     static __device__ __forceinline__ __half2 adjoint2(__half2 x, __half2 adjz) { return select_gt0(x, adjz, __float2half2_rn(0.f)); }
     static __device__ __forceinline__ half forward(half x) { return __hgt(x, hZERO()) ? x : hZERO(); }
     static __device__ __forceinline__ half adjoint(half x, half adjz) { return __hgt(x, hZERO()) ? adjz : hZERO(); }
+    // rounding and clamping in one conversion instruction (a NaN input stays NaN here; the comparison form gives 0)
+    static __device__ __forceinline__ __half2 forward_f32x2(float a, float b)
+    {
+        uint32_t r;
+        asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+        return *reinterpret_cast<__half2*>(&r);
+    }
 };
 
 // "z = __hgt(x, hZERO()) ? x : __hsub(hexp(x), 1)" / "adjx = __hgt(x, hZERO()) ? adjz : __hmul(adjz, hexp(x))"
@@ -67,6 +76,13 @@ struct BuiltinCelu {
     }
     static __device__ __forceinline__ half forward(half x) { return __hgt(x, hZERO()) ? x : __hsub(hexp(x), __float2half(1.0f)); }
     static __device__ __forceinline__ half adjoint(half x, half adjz) { return __hgt(x, hZERO()) ? adjz : __hmul(adjz, hexp(x)); }
+    static __device__ __forceinline__ float celu_f32(float x)
+    {
+        float e;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 1.4426950408889634f));
+        return x > 0.f ? x : e - 1.f;
+    }
+    static __device__ __forceinline__ __half2 forward_f32x2(float a, float b) { return __floats2half2_rn(celu_f32(a), celu_f32(b)); }
 };
 
 // "z = hsin(x)" / "adjx = __hmul(hcos(x), adjz)"
@@ -85,6 +101,7 @@ struct BuiltinSine {
     }
     static __device__ __forceinline__ half forward(half x) { return hsin(x); }
     static __device__ __forceinline__ half adjoint(half x, half adjz) { return __hmul(hcos(x), adjz); }
+    static __device__ __forceinline__ __half2 forward_f32x2(float a, float b) { return __floats2half2_rn(__sinf(a), __sinf(b)); }
 };
 
 // "z = x" / "adjx = adjz"
@@ -93,6 +110,7 @@ struct BuiltinIdentity {
     static __device__ __forceinline__ __half2 adjoint2(__half2, __half2 adjz) { return adjz; }
     static __device__ __forceinline__ half forward(half x) { return x; }
     static __device__ __forceinline__ half adjoint(half, half adjz) { return adjz; }
+    static __device__ __forceinline__ __half2 forward_f32x2(float a, float b) { return __floats2half2_rn(a, b); }
 };
 
 } // namespace kernel

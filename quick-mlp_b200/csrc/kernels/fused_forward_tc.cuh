@@ -5,15 +5,16 @@
 // machine mapping:
 //   * one persistent CTA per SM; all weight matrices are staged once in shared memory in the K-major, 128-byte
 //     swizzled operand layout the tensor core reads through a shared-memory descriptor;
-//   * SLOTS point tiles of 128 points are in flight per CTA. Each slot owns one warpgroup (128 threads, one thread per
-//     point = one TMEM lane), one activation operand buffer in shared memory, and one fp32 accumulator in tensor memory;
-//   * one extra warp issues the MMAs: for slot s and layer l, K/16 instructions D(128 x Cout) (+)= A(128 x 16) * W^T,
-//     then tcgen05.commit signals the slot's "accumulator full" mbarrier;
-//   * the slot's warpgroup waits for that barrier, reads its accumulator row with tcgen05.ld, rounds to half, adds the
-//     bias, applies the activation, writes the row of the next layer's A operand (swizzled) and signals "operand ready".
-//     The epilogue of one slot overlaps the MMAs and epilogues of the others.
-// Every wait is bounded: on a timeout the CTA raises an abort flag, all loops drain, tensor memory is released and the
-// kernel reports through LaunchArgs::status instead of hanging.
+//   * the CTA consists of up to four warpgroups of 128 threads. A warpgroup owns one or two tile slots; a slot is one
+//     tile of 128 points in flight: an activation operand buffer in shared memory plus an fp32 accumulator in tensor
+//     memory. One thread = one point = one TMEM lane;
+//   * per layer the warpgroup writes the rows of the A operand, synchronises on a named barrier, and one of its threads
+//     issues K/16 MMAs D(128 x Cout) (+)= A(128 x 16) * W^T followed by tcgen05.commit onto the slot's mbarrier;
+//   * the warpgroup waits on that mbarrier, reads its accumulator row with tcgen05.ld, rounds to half, adds the bias,
+//     applies the activation and writes the row of the next layer's operand. With two slots it alternates between the
+//     two tiles, so the MMAs of one run under the epilogue of the other; the warpgroups overlap each other anyway.
+// Every mbarrier wait is bounded, and every stage ends in a warpgroup-wide vote: on a timeout the whole warpgroup leaves
+// together, the CTA drains, tensor memory is released and the kernel reports through LaunchArgs::status.
 #pragma once
 #include "fused_network.cuh"
 
@@ -28,10 +29,6 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
 {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
-__device__ __forceinline__ void mbar_arrive(uint32_t bar)
-{
-    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(bar) : "memory");
-}
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity)
 {
     uint32_t ok;
@@ -39,15 +36,20 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity)
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// bounded wait; returns false (and raises the abort flag) on timeout or when another thread aborted
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abortFlag)
+// bounded wait; false on timeout
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
 {
-    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
+    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i)
         if (mbar_test(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abortFlag) return false;
-    }
-    *abortFlag = 1;
     return false;
+}
+// barrier over the 128 threads of one warpgroup that also AND-reduces a predicate
+__device__ __forceinline__ bool warpgroup_vote(int barrierId, bool pred)
+{
+    uint32_t r;
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %2, 0;\n\tbar.red.and.pred q, %1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                 : "=r"(r) : "r"(barrierId), "r"(static_cast<uint32_t>(pred)) : "memory");
+    return r != 0;
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -83,6 +85,26 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16])
                  : "r"(taddr) : "memory");
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// 64 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64])
+{
+    uint32_t r[64];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,"
+        "%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+          "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]),
+          "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]),
+          "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]),
+          "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+        : "r"(taddr) : "memory");
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
 }
 
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart.
@@ -134,40 +156,53 @@ struct TcLayout {
         return m;
     }
     __host__ __device__ static constexpr int aBytes() { return (maxCin() + 63) / 64 * TC_TILE * 128; }
-    __host__ __device__ static constexpr int biasHalfs()
-    {
-        int o = 0;
-        for (int i = 0; i < NL; ++i) o += Spec::COUT[i];
-        return o;
-    }
+    // Bias operands. The bias is added by the tensor core: one extra K=16 MMA per biased layer whose A operand is a
+    // constant block (every row = [1, 0, ..., 0], shared by all slots and layers) and whose B operand holds the bias in
+    // its first K column. Both are K-major blocks of 16 halfs per row in the un-swizzled canonical layout
+    // (8-row x 16-byte core matrices; see bias_block_offset).
+    __host__ __device__ static constexpr int onesBytes() { return TC_TILE * 32; }
     __host__ __device__ static constexpr int biasOffset(int l)
     {
-        int o = 0;
-        for (int i = 0; i < l; ++i) o += Spec::COUT[i];
+        int o = onesBytes();
+        for (int i = 0; i < l; ++i) o += Spec::COUT[i] * 32;
         return o;
     }
+    __host__ __device__ static constexpr int biasBytes() { return biasOffset(NL); }
     // accumulator columns per slot: power of two >= 32 so that SLOTS * cols is a legal allocation size
     __host__ __device__ static constexpr int accCols() { return maxCout() <= 32 ? 32 : maxCout() <= 64 ? 64 : maxCout() <= 128 ? 128 : 256; }
-    __host__ __device__ static constexpr int slots()
-    {
-        int s = 4;
-        while (s > 1 && (s * accCols() > 512 || weightBytes() + s * aBytes() + 4096 > 220 * 1024)) s >>= 1;
-        return s;
-    }
+    __host__ __device__ static constexpr bool fits(int s) { return s * accCols() <= 512 && weightBytes() + s * aBytes() + biasBytes() + 4096 <= 220 * 1024; }
+    __host__ __device__ static constexpr int warpgroups() { return fits(4) ? 4 : fits(2) ? 2 : 1; }
+    __host__ __device__ static constexpr int slotsPerWarpgroup() { return fits(2 * warpgroups()) ? 2 : 1; }
+    __host__ __device__ static constexpr int slots() { return warpgroups() * slotsPerWarpgroup(); }
     __host__ __device__ static constexpr bool eligible()
     {
-        return maxCout() <= 128 && maxCin() <= 128 && weightBytes() + aBytes() + 4096 <= 220 * 1024;
+        return maxCout() <= 128 && maxCin() <= 128 && fits(1);
     }
     __host__ __device__ static constexpr int aStart() { return weightBytes(); }
     __host__ __device__ static constexpr int biasStart() { return aStart() + slots() * aBytes(); }
-    __host__ __device__ static constexpr int barStart() { return (biasStart() + biasHalfs() * 2 + 15) / 16 * 16; }
-    // 16 mbarriers (8 "full" + 8 "ready" slots) of 8 bytes, the TMEM base word and the abort flag, 1 KB alignment slack
-    __host__ __device__ static constexpr int totalBytes() { return barStart() + 16 * 8 + 64 + 1024; }
+    __host__ __device__ static constexpr int barStart() { return (biasStart() + biasBytes() + 127) / 128 * 128; }
+    // 8 mbarriers of 8 bytes, the TMEM base word and the abort flag, 1 KB alignment slack
+    __host__ __device__ static constexpr int totalBytes() { return barStart() + 8 * 8 + 64 + 1024; }
 };
 
-// weights of layer L -> swizzled K-major operand in shared memory (whole CTA)
+// byte offset of element (row, k) of a K-major block of 16 halfs per row in the un-swizzled canonical layout:
+// core matrices of 8 rows x 16 bytes (128 contiguous bytes); the two core matrices of a row group (k 0-7, k 8-15) are
+// adjacent (leading byte offset 128), row groups are 256 bytes apart (stride byte offset 256)
+__device__ __forceinline__ uint32_t bias_block_offset(int row, int k)
+{
+    return static_cast<uint32_t>((row >> 3) * 256 + (k >> 3) * 128 + (row & 7) * 16 + (k & 7) * 2);
+}
+__device__ __forceinline__ uint64_t umma_desc_k16_noswizzle(uint32_t smemAddr)
+{
+    return static_cast<uint64_t>((smemAddr >> 4) & 0x3FFFu)   // start address, 16-byte units
+           | (8ull << 16)                                     // leading byte offset: 128 B between the two K halves
+           | (16ull << 32)                                    // stride byte offset: 256 B between 8-row groups
+           | (1ull << 46);                                    // descriptor version (sm_100); layout type 0 = no swizzle
+}
+
+// weights of layer L -> swizzled K-major operand in shared memory (whole CTA); bias -> first K column of its block
 template <class Spec, int L>
-__device__ __forceinline__ void tc_stage_weights(const LaunchArgs& p, unsigned char* sW, __half* sBias)
+__device__ __forceinline__ void tc_stage_weights(const LaunchArgs& p, unsigned char* sW, unsigned char* sBias)
 {
     if constexpr (L < Spec::NUM_LAYERS) {
         using TL = TcLayout<Spec>;
@@ -179,99 +214,46 @@ __device__ __forceinline__ void tc_stage_weights(const LaunchArgs& p, unsigned c
             const int r = i / CH, c = i % CH;
             *reinterpret_cast<uint4*>(dst + sw128_offset<COUT>(r, c)) = *reinterpret_cast<const uint4*>(gW + r * CIN + c * 8);
         }
-        for (int i = threadIdx.x; i < COUT; i += blockDim.x)
-            sBias[TL::biasOffset(L) + i] = Spec::BOFF[L] >= 0 ? p.weights[(Spec::BOFF[L] >= 0 ? Spec::BOFF[L] : 0) + i] : __ushort_as_half(0);
+        if constexpr (Spec::BOFF[L] >= 0) {
+            unsigned char* bb = sBias + TL::biasOffset(L);
+            for (int i = threadIdx.x; i < COUT * 16; i += blockDim.x) {
+                const int r = i >> 4, k = i & 15;
+                *reinterpret_cast<__half*>(bb + bias_block_offset(r, k)) = k == 0 ? p.weights[Spec::BOFF[L] + r] : __ushort_as_half(0);
+            }
+        }
         tc_stage_weights<Spec, L + 1>(p, sW, sBias);
     }
 }
 
-// MMA issue for one (slot, layer): K/16 instructions, then commit to the slot's "full" barrier (one thread)
+// MMAs of layer L for one slot: K/16 instructions, then commit onto the slot's mbarrier (issued by one thread)
 template <class Spec, int L>
-__device__ __forceinline__ void tc_issue_layer(int layer, uint32_t aBase, uint32_t wBase, uint32_t dTmem, uint32_t fullBar)
-{
-    if constexpr (L < Spec::NUM_LAYERS) {
-        if (layer == L) {
-            using TL = TcLayout<Spec>;
-            constexpr int CIN = Spec::CIN[L], COUT = Spec::COUT[L];
-            constexpr uint32_t idesc = umma_idesc_f16(TC_TILE, COUT);
-#pragma unroll
-            for (int k = 0; k < CIN / 16; ++k) {
-                const uint32_t aAddr = aBase + (k >> 2) * (TC_TILE * 128) + (k & 3) * 32;
-                const uint32_t bAddr = wBase + TL::wOffset(L) + (k >> 2) * (COUT * 128) + (k & 3) * 32;
-                umma_f16(dTmem, umma_desc_sw128(aAddr), umma_desc_sw128(bAddr), idesc, k > 0 ? 1u : 0u);
-            }
-            umma_commit(fullBar);
-        } else {
-            tc_issue_layer<Spec, L + 1>(layer, aBase, wBase, dTmem, fullBar);
-        }
-    }
-}
-
-// epilogue of layer L for one point row; returns false on abort
-template <class Spec, int L>
-__device__ __forceinline__ bool tc_epilogue_layers(const LaunchArgs& p, unsigned char* aBuf, const __half* sBias,
-                                                   uint32_t taddr, uint32_t fullBar, uint32_t readyBar, uint32_t& fullParity,
-                                                   int row, long long gRow, volatile int* abortFlag)
+__device__ __forceinline__ void tc_issue_layer(uint32_t aBase, uint32_t wBase, uint32_t biasBase, uint32_t dTmem, uint32_t fullBar)
 {
     using TL = TcLayout<Spec>;
-    using Act = typename Spec::template Act<L>;
-    constexpr int COUT = Spec::COUT[L];
-    constexpr bool LAST = L == Spec::NUM_LAYERS - 1;
-    constexpr bool BIAS = Spec::BOFF[L] >= 0;
-    // tcgen05.ld is warp-collective: the decision to go on must be the same for all 32 lanes
-    if (!__all_sync(0xffffffffu, mbar_wait(fullBar, fullParity, abortFlag))) return false;
-    fullParity ^= 1u;
-    tc_fence_after();
-    const __half* bias = sBias + TL::biasOffset(L);
-    constexpr int NCH = LAST ? (Spec::NUM_OUTPUTS + 15) / 16 : COUT / 16;   // 16-column groups that are needed
+    constexpr int CIN = Spec::CIN[L], COUT = Spec::COUT[L];
+    constexpr uint32_t idesc = umma_idesc_f16(TC_TILE, COUT);
 #pragma unroll
-    for (int g0 = 0; g0 < NCH; g0 += 4) {
-      // up to 64 accumulator columns in flight, one wait
-      float vv[4][16];
-#pragma unroll
-      for (int gg = 0; gg < 4; ++gg)
-          if (g0 + gg < NCH) tmem_ld16(taddr + (g0 + gg) * 16, vv[gg]);
-      tmem_wait_ld();
-#pragma unroll
-      for (int gg = 0; gg < 4; ++gg) {
-        const int g = g0 + gg;
-        if (g >= NCH) continue;
-        float (&v)[16] = vv[gg];
-        uint32_t packed[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
-            if constexpr (BIAS) h = __hadd2(h, *reinterpret_cast<const __half2*>(bias + g * 16 + 2 * i));
-            h = Act::forward2(h);
-            packed[i] = h2_as_u32(h);
-        }
-        if constexpr (!LAST) {
-            // row of the next layer's A operand: two 16-byte chunks
-            *reinterpret_cast<uint4*>(aBuf + sw128_offset<TC_TILE>(row, 2 * g)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            *reinterpret_cast<uint4*>(aBuf + sw128_offset<TC_TILE>(row, 2 * g + 1)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-        } else {
-            if (gRow < p.numel) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float2 f = __half22float2(u32_as_h2(packed[i]));
-                    const int c = g * 16 + 2 * i;
-                    if (c < Spec::NUM_OUTPUTS) p.output[gRow * p.outS0 + c * p.outS1] = f.x;
-                    if (c + 1 < Spec::NUM_OUTPUTS) p.output[gRow * p.outS0 + (c + 1) * p.outS1] = f.y;
-                }
-            }
-        }
-      }
+    for (int k = 0; k < CIN / 16; ++k) {
+        const uint32_t aAddr = aBase + (k >> 2) * (TC_TILE * 128) + (k & 3) * 32;
+        const uint32_t bAddr = wBase + TL::wOffset(L) + (k >> 2) * (COUT * 128) + (k & 3) * 32;
+        umma_f16(dTmem, umma_desc_sw128(aAddr), umma_desc_sw128(bAddr), idesc, k > 0 ? 1u : 0u);
     }
-    if constexpr (!LAST) {
-        tc_fence_before();      // the accumulator reads are complete before the next MMA may overwrite it
-        fence_proxy_async();    // generic-proxy writes of the operand become visible to the tensor core
-        mbar_arrive(readyBar);
-        return tc_epilogue_layers<Spec, L + 1>(p, aBuf, sBias, taddr, fullBar, readyBar, fullParity, row, gRow, abortFlag);
-    } else {
-        tc_fence_before();
-        return true;
-    }
+    if constexpr (Spec::BOFF[L] >= 0)   // D += ones(128 x 16) * biasBlock(COUT x 16)^T : adds bias[n] to every row
+        umma_f16(dTmem, umma_desc_k16_noswizzle(biasBase), umma_desc_k16_noswizzle(biasBase + TL::biasOffset(L)), idesc, 1u);
+    umma_commit(fullBar);
 }
+
+// ---- one warpgroup, one thread per point row -----------------------------------------------------------------------
+struct TcSlot {                 // per-thread view of one tile slot
+    unsigned char* aBuf;        // activation operand buffer of the slot
+    uint32_t aAddr;             // its shared-memory address
+    uint32_t dTmem;             // TMEM address of the slot's accumulator (lane 0)
+    uint32_t taddr;             // TMEM address of this thread's accumulator row
+    uint32_t fullBar;           // mbarrier the MMAs of the slot commit to
+    uint32_t fullParity;
+    long long gRow;             // global point index of this thread in the slot's current tile
+    bool active;                // the slot has a tile in this round
+};
 
 struct TcRowWriter {   // encoded features of one point -> swizzled row of the A operand
     unsigned char* aBuf;
@@ -282,36 +264,129 @@ struct TcRowWriter {   // encoded features of one point -> swizzled row of the A
     }
 };
 
+// Stage 0: encode the point into the layer-0 operand. Stage L+1: epilogue of layer L. Each stage but the last ends
+// by launching the MMAs of the next layer. Returns false, for the whole warpgroup at once, when a wait timed out.
+template <class Spec, int ST>
+__device__ __forceinline__ bool tc_stage(const LaunchArgs& p, TcSlot& sl, uint32_t biasBase, uint32_t wBase, int row,
+                                         int barrierId, bool issuer)
+{
+    constexpr int NL = Spec::NUM_LAYERS;
+    bool ok = true;
+    if constexpr (ST == 0) {
+        constexpr int CIN0 = Spec::CIN[0];
+        // zero padding up to CIN0 and zero rows past the end of the batch
+#pragma unroll
+        for (int c = 0; c < CIN0 / 8; ++c) *reinterpret_cast<uint4*>(sl.aBuf + sw128_offset<TC_TILE>(row, c)) = make_uint4(0, 0, 0, 0);
+        if (sl.gRow < p.numel) {
+            RowReader in{p.input + sl.gRow * p.inS0, p.inS1};
+            encode_point<Spec, 0>(p, in, TcRowWriter{sl.aBuf, row});
+        }
+    } else {
+        constexpr int L = ST - 1;
+        using Act = typename Spec::template Act<L>;
+        constexpr int COUT = Spec::COUT[L];
+        constexpr bool LAST = L == NL - 1;
+        // tcgen05.ld is warp-collective: the decision to go on must be the same for all 32 lanes
+        ok = __all_sync(0xffffffffu, mbar_wait(sl.fullBar, sl.fullParity));
+        sl.fullParity ^= 1u;
+        if (ok) {
+            tc_fence_after();
+            constexpr int NCOL = LAST ? (Spec::NUM_OUTPUTS + 15) / 16 * 16 : COUT;   // accumulator columns that are needed
+#pragma unroll
+            for (int c0 = 0; c0 < NCOL; c0 += 64) {
+                float v[64];   // up to 64 accumulator columns (bias already added by the tensor core), one wait
+                if (NCOL - c0 >= 64) tmem_ld64(sl.taddr + c0, v);
+                else {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g)
+                        if (c0 + g * 16 < NCOL) tmem_ld16(sl.taddr + c0 + g * 16, *reinterpret_cast<float (*)[16]>(&v[g * 16]));
+                }
+                tmem_wait_ld();
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    if (c0 + g * 16 >= NCOL) continue;
+                    uint32_t packed[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) packed[i] = h2_as_u32(Act::forward_f32x2(v[g * 16 + 2 * i], v[g * 16 + 2 * i + 1]));
+                    const int chunk = (c0 + g * 16) / 8;
+                    if constexpr (!LAST) {
+                        // row of the next layer's A operand: two 16-byte chunks
+                        *reinterpret_cast<uint4*>(sl.aBuf + sw128_offset<TC_TILE>(row, chunk)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        *reinterpret_cast<uint4*>(sl.aBuf + sw128_offset<TC_TILE>(row, chunk + 1)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    } else if (sl.gRow < p.numel) {
+                        // first NUM_OUTPUTS channels -> fp32 (kernels/network_forward.cuh:103-111)
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float2 f = __half22float2(u32_as_h2(packed[i]));
+                            const int c = c0 + g * 16 + 2 * i;
+                            if (c < Spec::NUM_OUTPUTS) p.output[sl.gRow * p.outS0 + c * p.outS1] = f.x;
+                            if (c + 1 < Spec::NUM_OUTPUTS) p.output[sl.gRow * p.outS0 + (c + 1) * p.outS1] = f.y;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    // All 128 rows of the operand are written and all accumulator reads are complete before the next MMAs start;
+    // the same barrier carries the vote that makes a timeout a decision of the whole warpgroup.
+    tc_fence_before();
+    fence_proxy_async();    // generic-proxy writes of the operand become visible to the tensor core
+    ok = warpgroup_vote(barrierId, ok);
+    if constexpr (ST < NL) {
+        if (ok && issuer) {
+            tc_fence_after();
+            tc_issue_layer<Spec, ST>(sl.aAddr, wBase, biasBase, sl.dTmem, sl.fullBar);
+        }
+    }
+    return ok;
+}
+
+// all stages of up to SPW tiles, interleaved stage by stage
+template <class Spec, int ST, int SPW>
+__device__ __forceinline__ bool tc_run_stages(const LaunchArgs& p, TcSlot (&sl)[SPW], uint32_t biasBase, uint32_t wBase, int row,
+                                              int barrierId, bool issuer)
+{
+    if constexpr (ST <= Spec::NUM_LAYERS) {
+#pragma unroll
+        for (int j = 0; j < SPW; ++j)
+            if (sl[j].active) {   // uniform over the warpgroup
+                if (!tc_stage<Spec, ST>(p, sl[j], biasBase, wBase, row, barrierId, issuer)) return false;
+            }
+        return tc_run_stages<Spec, ST + 1, SPW>(p, sl, biasBase, wBase, row, barrierId, issuer);
+    } else {
+        return true;
+    }
+}
+
 template <class Spec>
-__global__ void __launch_bounds__(TcLayout<Spec>::slots() * 128 + 32, 1)
+__global__ void __launch_bounds__(TcLayout<Spec>::warpgroups() * 128, 1)
 fused_forward_tc_kernel(const __grid_constant__ LaunchArgs p)
 {
     using TL = TcLayout<Spec>;
     constexpr int SLOTS = TL::slots();
-    constexpr int NL = Spec::NUM_LAYERS;
+    constexpr int SPW = TL::slotsPerWarpgroup();
+    static_assert(SLOTS <= 8, "barrier area holds 8 slots");
     extern __shared__ unsigned char smemRaw[];
     // the swizzled operand layout needs 1024-byte alignment of every operand base
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~static_cast<uintptr_t>(1023));
     unsigned char* sW = smem;
     unsigned char* sA = smem + TL::aStart();
-    __half* sBias = reinterpret_cast<__half*>(smem + TL::biasStart());
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TL::barStart());   // [SLOTS] full, [SLOTS] ready
-    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 16);
-    volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
+    unsigned char* sBias = smem + TL::biasStart();   // [ones block | bias block per layer]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TL::barStart());   // one per slot
+    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 8);
+    int* abortFlag = reinterpret_cast<int*>(tmemSlot + 1);
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr int MMA_WARP = SLOTS * 4;
+    const int warp = threadIdx.x >> 5;
 
     tc_stage_weights<Spec, 0>(p, sW, sBias);
+    for (int i = threadIdx.x; i < TC_TILE * 16; i += blockDim.x)   // constant A operand of the bias MMA: every row = [1, 0, ..., 0]
+        *reinterpret_cast<__half*>(sBias + bias_block_offset(i >> 4, i & 15)) = (i & 15) == 0 ? __ushort_as_half(0x3C00) : __ushort_as_half(0);
     if (threadIdx.x == 0) {
         *abortFlag = 0;
-        for (int s = 0; s < SLOTS; ++s) {
-            mbar_init(smem_u32(bars + s), 1);            // full: one tcgen05.commit
-            mbar_init(smem_u32(bars + 8 + s), 128);      // ready: every thread of the warpgroup
-        }
+        for (int s = 0; s < SLOTS; ++s) mbar_init(smem_u32(bars + s), 1);   // one tcgen05.commit per phase
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == MMA_WARP) {
+    if (warp == 0) {
         tmem_alloc(smem_u32(tmemSlot), SLOTS * TL::accCols());
         tmem_relinquish();
     }
@@ -321,75 +396,41 @@ fused_forward_tc_kernel(const __grid_constant__ LaunchArgs p)
     tc_fence_after();
     const uint32_t tmemBase = *tmemSlot;
 
+    // tile i of this CTA's sequence (global tile blockIdx.x + i * gridDim.x) goes to slot i % SLOTS
     const long long numTiles = (p.numel + TC_TILE - 1) / TC_TILE;
-    // tile t of this CTA's sequence goes to slot t % SLOTS
     const long long firstTile = blockIdx.x;
     const long long stride = gridDim.x;
-    long long myTiles = firstTile < numTiles ? (numTiles - firstTile + stride - 1) / stride : 0;
+    const long long myTiles = firstTile < numTiles ? (numTiles - firstTile + stride - 1) / stride : 0;
 
-    if (warp < MMA_WARP) {
-        // ---------------- epilogue warpgroup of slot s ----------------
-        const int s = warp >> 2;
-        const int row = threadIdx.x & 127;                       // point row inside the tile = TMEM lane
-        unsigned char* aBuf = sA + s * TL::aBytes();
-        const uint32_t fullBar = smem_u32(bars + s), readyBar = smem_u32(bars + 8 + s);
-        const uint32_t taddr = tmemBase + (static_cast<uint32_t>((warp & 3) * 32) << 16) + s * TL::accCols();
-        uint32_t fullParity = 0;
-        bool ok = true;
-        for (long long i = s; i < myTiles && ok; i += SLOTS) {
-            const long long tile = firstTile + i * stride;
-            const long long gRow = tile * TC_TILE + row;
-            // layer-0 operand: encodings of this thread's point (zero padding up to CIN0, zero rows past the end)
-            constexpr int CIN0 = Spec::CIN[0];
+    const int wg = warp >> 2;
+    const int row = threadIdx.x & 127;                       // point row inside the tile = TMEM lane
+    const bool issuer = row == 0;
+    const uint32_t wBase = smem_u32(sW), biasBase = smem_u32(sBias);
+    TcSlot sl[SPW];
 #pragma unroll
-            for (int c = 0; c < CIN0 / 8; ++c) *reinterpret_cast<uint4*>(aBuf + sw128_offset<TC_TILE>(row, c)) = make_uint4(0, 0, 0, 0);
-            if (gRow < p.numel) {
-                RowReader in{p.input + gRow * p.inS0, p.inS1};
-                encode_point<Spec, 0>(p, in, TcRowWriter{aBuf, row});
-            }
-            tc_fence_before();
-            fence_proxy_async();
-            mbar_arrive(readyBar);
-            ok = tc_epilogue_layers<Spec, 0>(p, aBuf, sBias, taddr, fullBar, readyBar, fullParity, row, gRow, abortFlag);
-        }
-    } else if (lane == 0) {
-        // ---------------- MMA issue thread ----------------
-        const uint32_t aBase = smem_u32(sA), wBase = smem_u32(sW);
-        int layer[SLOTS];
-        long long done[SLOTS];          // tiles finished per slot
-        uint32_t readyParity[SLOTS];
-        long long total = 0;
-#pragma unroll
-        for (int s = 0; s < SLOTS; ++s) {
-            layer[s] = 0; done[s] = 0; readyParity[s] = 0;
-        }
-        long long perSlot[SLOTS];
-#pragma unroll
-        for (int s = 0; s < SLOTS; ++s) { perSlot[s] = myTiles > s ? (myTiles - s + SLOTS - 1) / SLOTS : 0; total += perSlot[s] * NL; }
-        long long issued = 0;
-        uint32_t idle = 0;
-        while (issued < total) {
-            bool any = false;
-#pragma unroll
-            for (int s = 0; s < SLOTS; ++s) {
-                if (done[s] >= perSlot[s]) continue;
-                if (!mbar_test(smem_u32(bars + 8 + s), readyParity[s])) continue;
-                readyParity[s] ^= 1u;
-                tc_fence_after();
-                tc_issue_layer<Spec, 0>(layer[s], aBase + s * TL::aBytes(), wBase, tmemBase + s * TL::accCols(), smem_u32(bars + s));
-                ++issued;
-                any = true;
-                if (++layer[s] == NL) { layer[s] = 0; ++done[s]; }
-            }
-            if (any) { idle = 0; continue; }
-            if (++idle > TC_SPIN_LIMIT) { *abortFlag = 1; break; }
-            if ((idle & 1023u) == 1023u && *abortFlag) break;
-        }
+    for (int j = 0; j < SPW; ++j) {
+        const int s = wg * SPW + j;
+        sl[j].aBuf = sA + s * TL::aBytes();
+        sl[j].aAddr = smem_u32(sl[j].aBuf);
+        sl[j].fullBar = smem_u32(bars + s);
+        sl[j].dTmem = tmemBase + s * TL::accCols();
+        sl[j].taddr = sl[j].dTmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+        sl[j].fullParity = 0;
     }
-    // drain: every role reaches this point (all waits are bounded), then tensor memory is released
+    bool ok = true;
+    for (long long i = static_cast<long long>(wg) * SPW; i < myTiles && ok; i += SLOTS) {
+#pragma unroll
+        for (int j = 0; j < SPW; ++j) {
+            sl[j].active = i + j < myTiles;
+            sl[j].gRow = (firstTile + (i + j) * stride) * TC_TILE + row;
+        }
+        ok = tc_run_stages<Spec, 0, SPW>(p, sl, biasBase, wBase, row, 1 + wg, issuer);
+    }
+    if (!ok) *abortFlag = 1;
+    // drain: every warpgroup reaches this point (all waits are bounded), then tensor memory is released
     tc_fence_before();
     __syncthreads();
-    if (warp == MMA_WARP) {
+    if (warp == 0) {
         tc_fence_after();
         tmem_dealloc(tmemBase, SLOTS * TL::accCols());
     }
@@ -402,7 +443,7 @@ struct TcLaunchers {
     {
         using TL = TcLayout<Spec>;
         constexpr int smem = TL::totalBytes();
-        constexpr int threads = TL::slots() * 128 + 32;
+        constexpr int threads = TL::warpgroups() * 128;
         static bool configured = false;
         auto k = fused_forward_tc_kernel<Spec>;
         if (!configured) {
