@@ -171,8 +171,14 @@ struct TcLayout {
     // accumulator columns per slot: power of two >= 32 so that SLOTS * cols is a legal allocation size
     __host__ __device__ static constexpr int accCols() { return maxCout() <= 32 ? 32 : maxCout() <= 64 ? 64 : maxCout() <= 128 ? 128 : 256; }
     __host__ __device__ static constexpr bool fits(int s) { return s * accCols() <= 512 && weightBytes() + s * aBytes() + biasBytes() + 4096 <= 220 * 1024; }
-    __host__ __device__ static constexpr int warpgroups() { return fits(4) ? 4 : fits(2) ? 2 : 1; }
-    __host__ __device__ static constexpr int slotsPerWarpgroup() { return fits(2 * warpgroups()) ? 2 : 1; }
+#ifndef QMLP_TC_MAX_WARPGROUPS
+#define QMLP_TC_MAX_WARPGROUPS 8
+#endif
+    // 8 warpgroups (1024 threads, 64 registers each) with one slot each, or up to 4 warpgroups (128 registers) that
+    // alternate between two slots when shared and tensor memory allow
+    __host__ __device__ static constexpr int warpgroups() { return (QMLP_TC_MAX_WARPGROUPS >= 8 && fits(8)) ? 8 : fits(4) ? 4 : fits(2) ? 2 : 1; }
+    __host__ __device__ static constexpr int slotsPerWarpgroup() { return warpgroups() < 8 && fits(2 * warpgroups()) ? 2 : 1; }
+    __host__ __device__ static constexpr int loadWidth() { return warpgroups() == 8 ? 32 : 64; }
     __host__ __device__ static constexpr int slots() { return warpgroups() * slotsPerWarpgroup(); }
     __host__ __device__ static constexpr bool eligible()
     {
@@ -227,26 +233,28 @@ __device__ __forceinline__ void tc_stage_weights(const LaunchArgs& p, unsigned c
 
 // MMAs of layer L for one slot: K/16 instructions, then commit onto the slot's mbarrier (issued by one thread)
 template <class Spec, int L>
-__device__ __forceinline__ void tc_issue_layer(uint32_t aBase, uint32_t wBase, uint32_t biasBase, uint32_t dTmem, uint32_t fullBar)
+// The descriptors differ from call to call only in the 14-bit start-address field (low word, 16-byte units), so the
+// issuing thread keeps three base descriptors and adds compile-time offsets.
+__device__ __forceinline__ void tc_issue_layer(uint64_t aDesc0, uint64_t wDesc0, uint64_t biasDesc0, uint32_t dTmem, uint32_t fullBar)
 {
     using TL = TcLayout<Spec>;
     constexpr int CIN = Spec::CIN[L], COUT = Spec::COUT[L];
     constexpr uint32_t idesc = umma_idesc_f16(TC_TILE, COUT);
 #pragma unroll
     for (int k = 0; k < CIN / 16; ++k) {
-        const uint32_t aAddr = aBase + (k >> 2) * (TC_TILE * 128) + (k & 3) * 32;
-        const uint32_t bAddr = wBase + TL::wOffset(L) + (k >> 2) * (COUT * 128) + (k & 3) * 32;
-        umma_f16(dTmem, umma_desc_sw128(aAddr), umma_desc_sw128(bAddr), idesc, k > 0 ? 1u : 0u);
+        const uint64_t aOff = static_cast<uint64_t>(((k >> 2) * (TC_TILE * 128) + (k & 3) * 32) >> 4);
+        const uint64_t bOff = static_cast<uint64_t>((TL::wOffset(L) + (k >> 2) * (COUT * 128) + (k & 3) * 32) >> 4);
+        umma_f16(dTmem, aDesc0 + aOff, wDesc0 + bOff, idesc, k > 0 ? 1u : 0u);
     }
     if constexpr (Spec::BOFF[L] >= 0)   // D += ones(128 x 16) * biasBlock(COUT x 16)^T : adds bias[n] to every row
-        umma_f16(dTmem, umma_desc_k16_noswizzle(biasBase), umma_desc_k16_noswizzle(biasBase + TL::biasOffset(L)), idesc, 1u);
+        umma_f16(dTmem, biasDesc0, biasDesc0 + static_cast<uint64_t>(TL::biasOffset(L) >> 4), idesc, 1u);
     umma_commit(fullBar);
 }
 
 // ---- one warpgroup, one thread per point row -----------------------------------------------------------------------
 struct TcSlot {                 // per-thread view of one tile slot
     unsigned char* aBuf;        // activation operand buffer of the slot
-    uint32_t aAddr;             // its shared-memory address
+    uint64_t aDesc0;            // operand descriptor of its first K step
     uint32_t dTmem;             // TMEM address of the slot's accumulator (lane 0)
     uint32_t taddr;             // TMEM address of this thread's accumulator row
     uint32_t fullBar;           // mbarrier the MMAs of the slot commit to
@@ -267,7 +275,7 @@ struct TcRowWriter {   // encoded features of one point -> swizzled row of the A
 // Stage 0: encode the point into the layer-0 operand. Stage L+1: epilogue of layer L. Each stage but the last ends
 // by launching the MMAs of the next layer. Returns false, for the whole warpgroup at once, when a wait timed out.
 template <class Spec, int ST>
-__device__ __forceinline__ bool tc_stage(const LaunchArgs& p, TcSlot& sl, uint32_t biasBase, uint32_t wBase, int row,
+__device__ __forceinline__ bool tc_stage(const LaunchArgs& p, TcSlot& sl, uint64_t biasDesc0, uint64_t wDesc0, int row,
                                          int barrierId, bool issuer)
 {
     constexpr int NL = Spec::NUM_LAYERS;
@@ -293,17 +301,18 @@ __device__ __forceinline__ bool tc_stage(const LaunchArgs& p, TcSlot& sl, uint32
             tc_fence_after();
             constexpr int NCOL = LAST ? (Spec::NUM_OUTPUTS + 15) / 16 * 16 : COUT;   // accumulator columns that are needed
 #pragma unroll
-            for (int c0 = 0; c0 < NCOL; c0 += 64) {
-                float v[64];   // up to 64 accumulator columns (bias already added by the tensor core), one wait
-                if (NCOL - c0 >= 64) tmem_ld64(sl.taddr + c0, v);
+            constexpr int LDW = TcLayout<Spec>::loadWidth();   // accumulator columns fetched per wait
+            for (int c0 = 0; c0 < NCOL; c0 += LDW) {
+                float v[LDW];   // bias already added by the tensor core
+                if (LDW == 64 && NCOL - c0 >= 64) tmem_ld64(sl.taddr + c0, *reinterpret_cast<float (*)[64]>(&v[0]));
                 else {
 #pragma unroll
-                    for (int g = 0; g < 4; ++g)
+                    for (int g = 0; g < LDW / 16; ++g)
                         if (c0 + g * 16 < NCOL) tmem_ld16(sl.taddr + c0 + g * 16, *reinterpret_cast<float (*)[16]>(&v[g * 16]));
                 }
                 tmem_wait_ld();
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
+                for (int g = 0; g < LDW / 16; ++g) {
                     if (c0 + g * 16 >= NCOL) continue;
                     uint32_t packed[8];
 #pragma unroll
@@ -335,7 +344,7 @@ __device__ __forceinline__ bool tc_stage(const LaunchArgs& p, TcSlot& sl, uint32
     if constexpr (ST < NL) {
         if (ok && issuer) {
             tc_fence_after();
-            tc_issue_layer<Spec, ST>(sl.aAddr, wBase, biasBase, sl.dTmem, sl.fullBar);
+            tc_issue_layer<Spec, ST>(sl.aDesc0, wDesc0, biasDesc0, sl.dTmem, sl.fullBar);
         }
     }
     return ok;
@@ -343,16 +352,16 @@ __device__ __forceinline__ bool tc_stage(const LaunchArgs& p, TcSlot& sl, uint32
 
 // all stages of up to SPW tiles, interleaved stage by stage
 template <class Spec, int ST, int SPW>
-__device__ __forceinline__ bool tc_run_stages(const LaunchArgs& p, TcSlot (&sl)[SPW], uint32_t biasBase, uint32_t wBase, int row,
+__device__ __forceinline__ bool tc_run_stages(const LaunchArgs& p, TcSlot (&sl)[SPW], uint64_t biasDesc0, uint64_t wDesc0, int row,
                                               int barrierId, bool issuer)
 {
     if constexpr (ST <= Spec::NUM_LAYERS) {
 #pragma unroll
         for (int j = 0; j < SPW; ++j)
             if (sl[j].active) {   // uniform over the warpgroup
-                if (!tc_stage<Spec, ST>(p, sl[j], biasBase, wBase, row, barrierId, issuer)) return false;
+                if (!tc_stage<Spec, ST>(p, sl[j], biasDesc0, wDesc0, row, barrierId, issuer)) return false;
             }
-        return tc_run_stages<Spec, ST + 1, SPW>(p, sl, biasBase, wBase, row, barrierId, issuer);
+        return tc_run_stages<Spec, ST + 1, SPW>(p, sl, biasDesc0, wDesc0, row, barrierId, issuer);
     } else {
         return true;
     }
@@ -404,14 +413,16 @@ fused_forward_tc_kernel(const __grid_constant__ LaunchArgs p)
 
     const int wg = warp >> 2;
     const int row = threadIdx.x & 127;                       // point row inside the tile = TMEM lane
-    const bool issuer = row == 0;
-    const uint32_t wBase = smem_u32(sW), biasBase = smem_u32(sBias);
+    // the MMA-issuing thread of warpgroup wg sits in its warp (wg % 4), so the four issuers of a CTA run on four
+    // different SM sub-partitions instead of all on the first one
+    const bool issuer = row == (wg & 3) * 32;
+    const uint64_t wDesc0 = umma_desc_sw128(smem_u32(sW)), biasDesc0 = umma_desc_k16_noswizzle(smem_u32(sBias));
     TcSlot sl[SPW];
 #pragma unroll
     for (int j = 0; j < SPW; ++j) {
         const int s = wg * SPW + j;
         sl[j].aBuf = sA + s * TL::aBytes();
-        sl[j].aAddr = smem_u32(sl[j].aBuf);
+        sl[j].aDesc0 = umma_desc_sw128(smem_u32(sl[j].aBuf));
         sl[j].fullBar = smem_u32(bars + s);
         sl[j].dTmem = tmemBase + s * TL::accCols();
         sl[j].taddr = sl[j].dTmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
@@ -424,7 +435,7 @@ fused_forward_tc_kernel(const __grid_constant__ LaunchArgs p)
             sl[j].active = i + j < myTiles;
             sl[j].gRow = (firstTile + (i + j) * stride) * TC_TILE + row;
         }
-        ok = tc_run_stages<Spec, 0, SPW>(p, sl, biasBase, wBase, row, 1 + wg, issuer);
+        ok = tc_run_stages<Spec, 0, SPW>(p, sl, biasDesc0, wDesc0, row, 1 + wg, issuer);
     }
     if (!ok) *abortFlag = 1;
     // drain: every warpgroup reaches this point (all waits are bounded), then tensor memory is released
