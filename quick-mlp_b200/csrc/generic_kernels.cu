@@ -58,6 +58,11 @@ __global__ void __launch_bounds__(256) refresh_half_kernel(const float4* __restr
     }
 }
 
+// set to 1 by a kernel that gave up on a bounded on-chip wait; one copy per device context that loads the library
+static __device__ int g_statusWord;
+
+cudaError_t statusWordAddress(int** out) { return cudaGetSymbolAddress(reinterpret_cast<void**>(out), g_statusWord); }
+
 static unsigned gridFor(long long work, int numSMs)
 {
     long long blocks = (work + 255) / 256;

@@ -10,6 +10,8 @@ namespace kernel {
 cudaError_t launchAdam(float* master, float* grad, float* m, float* v, uint16_t* halfCopy, long long count,
                        float gradScale, float beta1, float beta2, float stepSize, float invSqrtBc2, float eps,
                        int numSMs, cudaStream_t stream);
+// Address, on the current device, of the library's kernel status word (a __device__ variable).
+cudaError_t statusWordAddress(int** out);
 cudaError_t launchRefreshHalf(const float* master, uint16_t* halfCopy, long long count, int numSMs, cudaStream_t stream);
 
 } // namespace kernel

@@ -17,6 +17,8 @@
 
 #include <cuda_runtime.h>
 
+#include "generic_kernels.h"
+
 namespace qmlp {
 
 Library& Library::instance()
@@ -101,11 +103,10 @@ int* Library::statusWord()
     if (cudaGetDevice(&dev) != cudaSuccess) throw cuda_error("cudaGetDevice failed: no CUDA device available");
     if (dev < 0 || dev >= 64) dev = 0;
     if (words[dev] == nullptr) {
-        // one 4-byte allocation per device for the life of the process, made at the first launch on that device
+        // the word is a __device__ variable of this library (zero at module load): nothing is allocated
         int* w = nullptr;
-        cudaError_t e = cudaMalloc(&w, sizeof(int));
-        if (e == cudaSuccess) e = cudaMemset(w, 0, sizeof(int));
-        if (e != cudaSuccess) throw cuda_error(std::string("status word allocation failed: ") + cudaGetErrorString(e));
+        cudaError_t e = kernel::statusWordAddress(&w);
+        if (e != cudaSuccess) throw cuda_error(std::string("status word lookup failed: ") + cudaGetErrorString(e));
         words[dev] = w;
     }
     return words[dev];
