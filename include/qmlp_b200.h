@@ -123,6 +123,16 @@ QMLP_API int qmlp_network_forward_memory(qmlp_network_t* net, int64_t num_elemen
 /* FusedNetwork::forward, src_cpp/src/fused_network.cpp:691-736 */
 QMLP_API int qmlp_network_forward(qmlp_network_t* net, const qmlp_tensor_t* input, qmlp_tensor_t* output,
                                   void* tmp_memory, qmlp_stream_t stream);
+/* Forward-with-stash without any allocation, for callers that cannot call cudaMalloc (a plug-in living on a fixed
+ * device-memory budget, a latency-critical loop that cannot take the synchronisation an allocation implies). It has no
+ * counterpart in the reference. Same kernel, arguments and output as qmlp_network_forward; the stash goes into one
+ * fixed device array of QMLP_STATIC_SCRATCH_BYTES that every GPU loading this library reserves until exit. A batch
+ * whose stash (qmlp_network_forward_memory) is larger is rejected with an error. All calls on a device share that
+ * array: it holds the last call's stash, and calls that overlap on the GPU race on it. The first call on a device
+ * resolves the array's address (and may load the network's kernels): make it before any stream capture. */
+#define QMLP_STATIC_SCRATCH_BYTES (32u << 20)
+QMLP_API int qmlp_network_forward_static_scratch(qmlp_network_t* net, const qmlp_tensor_t* input, qmlp_tensor_t* output,
+                                                 qmlp_stream_t stream);
 /* FusedNetwork::zeroGradients, src_cpp/src/fused_network.cpp:738-744 (asynchronous on `stream` here). */
 QMLP_API int qmlp_network_zero_gradients(qmlp_network_t* net, qmlp_stream_t stream);
 /* FusedNetwork::adjointMemory, src_cpp/src/fused_network.cpp:997-1010 */

@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIBDIR, "libqmlp_b200.so")
-SOURCES = ["host.cpp", "jit.cpp", "capi.cpp", "generic_kernels.cu"]
+SOURCES = ["host.cpp", "jit.cpp", "capi.cpp", "generic_kernels.cu", "static_scratch.cu"]
 NVCC = os.environ.get("QMLP_NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 

@@ -110,6 +110,26 @@ void launchNet(Network& n, int kernelId, const kernel::LaunchArgs& a, qmlp_strea
 
 } // namespace
 
+namespace qmlp {
+
+int reportError(int code, const char* message) { return fail(code, message ? message : ""); }
+
+void forwardWithStashAt(Network& n, const qmlp_tensor_t* input, qmlp_tensor_t* output, void* tmp, qmlp_stream_t stream)
+{
+    std::lock_guard<std::mutex> lock(n.mutex);
+    checkIO(n, input, output, "output");
+    if ((reinterpret_cast<uintptr_t>(tmp) & 15) != 0) throw std::runtime_error("stash memory must be 16-byte aligned");
+    kernel::LaunchArgs a;
+    fillCommon(n, a, input);
+    a.output = static_cast<float*>(output->data);
+    a.outS0 = output->strides[0];
+    a.outS1 = output->strides[1];
+    a.fwdTmp = static_cast<__half*>(tmp);
+    launchNet(n, kernel::KERNEL_FORWARD, a, stream);
+}
+
+} // namespace qmlp
+
 extern "C" {
 
 const char* qmlp_last_error(void) { return g_lastError.c_str(); }

@@ -216,6 +216,11 @@ private:
     std::map<unsigned, std::shared_ptr<KernelModule>> modules_;
 };
 
+// Used by entry points that live outside capi.cpp: record an error for qmlp_last_error() and return its code;
+// run forward-with-stash with the stash at `tmp` (argument checks and launch exactly as qmlp_network_forward).
+int reportError(int code, const char* message);
+void forwardWithStashAt(Network& net, const qmlp_tensor_t* input, qmlp_tensor_t* output, void* tmp, qmlp_stream_t stream);
+
 } // namespace qmlp
 
 // opaque C handles

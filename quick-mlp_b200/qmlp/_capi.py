@@ -71,6 +71,7 @@ SIGNATURES = {
     "qmlp_network_inference": (C.c_int, [_P, _TP, _TP, _P]),
     "qmlp_network_forward_memory": (C.c_int, [_P, C.c_int64, C.c_int, C.POINTER(C.c_size_t)]),
     "qmlp_network_forward": (C.c_int, [_P, _TP, _TP, _P, _P]),
+    "qmlp_network_forward_static_scratch": (C.c_int, [_P, _TP, _TP, _P]),
     "qmlp_network_zero_gradients": (C.c_int, [_P, _P]),
     "qmlp_network_adjoint_memory": (C.c_int, [_P, C.c_int64, C.c_int, C.POINTER(C.c_size_t)]),
     "qmlp_network_adjoint": (C.c_int, [_P, _TP, _TP, C.c_int, _TP, _P, _P, _P]),
