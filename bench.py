@@ -122,8 +122,17 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------------------------------------------------
+def host_threads():
+    """All host cores this process may use (torchrun exports OMP_NUM_THREADS=1, so OpenMP's default is not it)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_baseline(key, max_seconds=12.0, threads=0):
     """CPU restatement of the reference algorithm (oracle/cpu_ref.cpp, OpenMP) on a bounded sample of the workload."""
+    threads = threads or host_threads()
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import cpu_ref
     import helpers
@@ -148,11 +157,14 @@ def cpu_baseline(key, max_seconds=12.0, threads=0):
     sample = int(min(w["points"], max(probe, rate * max_seconds)))
     sample = 1 << int(np.floor(np.log2(sample)))
     x = helpers.uniform(42, 2, (sample, spec.num_inputs), w["lo"], w["hi"])
-    t0 = time.perf_counter(); net.forward(x, threads); dt = time.perf_counter() - t0
-    cores = threads if threads > 0 else cpu_ref.num_threads()
+    passes = int(max(1, min(64, rate * max_seconds / sample)))      # about max_seconds of CPU work in total
+    t0 = time.perf_counter()
+    for _ in range(passes):
+        net.forward(x, threads)
+    dt = time.perf_counter() - t0
     kind = "forward pass only" if w["mode"] == "train" else "fused inference"
-    return {"value": sample / dt, "unit": "points/s", "cores": cores, "kind": "port",
-            "sample": f"{sample} points of the workload ({kind}), {dt:.2f} s, C++/OpenMP restatement of the reference math"}
+    return {"value": sample * passes / dt, "unit": "points/s", "cores": threads, "kind": "port",
+            "sample": f"{passes} x {sample} points of the workload ({kind}), {dt:.2f} s, C++/OpenMP restatement of the reference math"}
 
 
 def run_reference_arm(args, rank, world):
@@ -176,10 +188,11 @@ def run_reference_arm(args, rank, world):
         else:
             tables.append(None)
     net = cpu_ref.CpuNetwork(spec, params, tables)
+    cores = host_threads()
     probe = 1 << 16
     x = helpers.uniform(42, 1, (probe, spec.num_inputs), w["lo"], w["hi"])
-    net.forward(x)
-    t0 = time.perf_counter(); net.forward(x); dt = time.perf_counter() - t0
+    net.forward(x, cores)
+    t0 = time.perf_counter(); net.forward(x, cores); dt = time.perf_counter() - t0
     rate = probe / max(dt, 1e-9)
     # each step: a bounded sample sized so the whole run stays within about two minutes
     budget = 100.0 / max(1, args.steps + args.warmup)
@@ -187,13 +200,12 @@ def run_reference_arm(args, rank, world):
     sample = 1 << int(np.floor(np.log2(sample)))
     x = helpers.uniform(42, 2, (sample, spec.num_inputs), w["lo"], w["hi"])
     for _ in range(args.warmup):
-        net.forward(x)
+        net.forward(x, cores)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        net.forward(x)
+        net.forward(x, cores)
     dt = time.perf_counter() - t0
     value = sample * args.steps / dt
-    cores = cpu_ref.num_threads()
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "points/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
