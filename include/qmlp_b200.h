@@ -81,7 +81,9 @@ QMLP_API const char* qmlp_get_kernel_cache_dir(void);
 QMLP_API int qmlp_set_kernel_include_dir(const char* dir);
 
 /* Kernel family used for fused inference: 0 = the best one instantiated for the spec (tcgen05 tensor-core kernel when
- * the layer widths allow it), 1 = the mma.sync kernels only. Takes the place of the reference's per-kernel tuning
+ * the layer widths allow it; a level-major encoding pass in front of it when the grid tables are much larger than L2,
+ * which makes the network keep a 2^18-point feature buffer from its first such call until it is destroyed),
+ * 1 = the mma.sync kernels only, 2 = the level-major pass for every grid network. Takes the place of the reference's per-kernel tuning
  * options (overwrite_blocksize_*, skew_shared_memory; src_cpp/src/fused_network.cpp:45-69). */
 QMLP_API int qmlp_set_kernel_path(int path);
 /* Synchronises the current device and returns (then clears) its kernel status word: 0 = every kernel ran to completion,

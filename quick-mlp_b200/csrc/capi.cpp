@@ -3,6 +3,7 @@
 #include "host.hpp"
 #include "generic_kernels.h"
 
+#include <algorithm>
 #include <cmath>
 #include <cstring>
 
@@ -169,7 +170,7 @@ int qmlp_set_kernel_include_dir(const char* dir) { Library::instance().includeDi
 int qmlp_set_kernel_path(int path)
 {
     QMLP_TRY
-    if (path != 0 && path != 1) throw std::runtime_error("kernel path must be 0 (best for the spec) or 1 (mma.sync only)");
+    if (path < 0 || path > 2) throw std::runtime_error("kernel path must be 0 (best for the spec), 1 (mma.sync only) or 2 (level-major grid pass)");
     Library::instance().kernelPath = path;
     QMLP_CATCH
 }
@@ -286,6 +287,41 @@ int qmlp_network_inference(qmlp_network_t* net, const qmlp_tensor_t* input, qmlp
     a.output = static_cast<float*>(output->data);
     a.outS0 = output->strides[0];
     a.outS1 = output->strides[1];
+    // Tables much larger than L2: encode level by level into planes, chunk by chunk, then run the layer chain on the
+    // planes (kernels/grid_planes.cuh). kernelPath 2 forces this path for any grid network.
+    const int path = Library::instance().kernelPath;
+    const bool wantPlanes = !n.planesUnsupported && a.numGrids > 0 && a.numel > 0 &&
+                            (path == 2 || (path == 0 && n.gridTableBytes() > (96ll << 20)));
+    if (wantPlanes) {
+        const int64_t cap = 1 << 18;
+        if (n.planes == nullptr) {
+            checkCuda(cudaMalloc(&n.planes, static_cast<size_t>(cap) * n.encodedChannels() * 2), "cudaMalloc(feature planes)");
+            n.planeCapacity = cap;
+        }
+        auto m = n.module(n.currentHalfMask());
+        const long long total = a.numel;
+        const float* in0 = a.input;
+        float* out0 = a.output;
+        bool ok = true;
+        for (long long c0 = 0; c0 < total && ok; c0 += n.planeCapacity) {
+            a.numel = std::min<long long>(n.planeCapacity, total - c0);
+            a.input = in0 + c0 * a.inS0;
+            a.output = out0 + c0 * a.outS0;
+            a.planes = static_cast<__half*>(n.planes);
+            a.planeStride = n.planeCapacity;
+            int launches = 0;
+            const int e = m->launch(kernel::KERNEL_ENCODE_PLANES, &a, static_cast<cudaStream_t>(stream), &launches);
+            if (e == static_cast<int>(cudaErrorNotSupported) && c0 == 0) { n.planesUnsupported = true; ok = false; break; }
+            checkLaunch(e, "kernel launch failed");
+            n.launchCount += launches;
+            checkLaunch(m->launch(kernel::KERNEL_INFERENCE_PLANES, &a, static_cast<cudaStream_t>(stream), &launches), "kernel launch failed");
+            n.launchCount += launches;
+        }
+        if (ok) return QMLP_OK;
+        a.numel = total;
+        a.input = in0;
+        a.output = out0;
+    }
     launchNet(n, kernel::KERNEL_INFERENCE, a, stream);
     QMLP_CATCH
 }

@@ -12,6 +12,7 @@
 #include <sys/stat.h>
 
 #include <cuda_fp16.h>
+#include <cuda_runtime.h>
 
 namespace qmlp {
 
@@ -460,6 +461,19 @@ Network::Network(const Json& cfg, const std::string& parent)
         if (l.useBias) { l.biasStart = numParameters_; numParameters_ += l.channelsOut; }
         else l.biasStart = -1;
     }
+}
+
+Network::~Network()
+{
+    if (planes != nullptr) cudaFree(planes);
+}
+
+int64_t Network::gridTableBytes() const
+{
+    int64_t b = 0;
+    for (const auto& e : encodings_)
+        if (e->isGrid() && e->paramInference.defined()) b += e->parameterCount() * (e->paramInference.precision == QMLP_HALF ? 2 : 4);
+    return b;
 }
 
 Encoding_ptr Network::encoding(int i) const

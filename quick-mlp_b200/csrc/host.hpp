@@ -202,6 +202,14 @@ public:
     void fillGrids(kernel::LaunchArgs& a) const;
     void clearModules();
 
+    ~Network();
+    int64_t gridTableBytes() const;   // bytes of all bound grid tables (what the gather walks through)
+    // level-major encoding pass (inference of networks with tables larger than L2): chunk buffer, allocated at the
+    // first such call and kept until the network is destroyed
+    void* planes = nullptr;
+    int64_t planeCapacity = 0;        // points per chunk
+    bool planesUnsupported = false;   // the spec has no instantiation of the plane kernels
+
     BoundTensor paramInference, paramGradients;
     std::vector<qmlp_encoding*> encodingHandles; // owned wrappers handed out through the C ABI
     int64_t launchCount = 0;

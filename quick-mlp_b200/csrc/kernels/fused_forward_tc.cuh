@@ -17,6 +17,7 @@
 // together, the CTA drains, tensor memory is released and the kernel reports through LaunchArgs::status.
 #pragma once
 #include "fused_network.cuh"
+#include "grid_planes.cuh"
 
 namespace qmlp {
 namespace kernel {
@@ -270,11 +271,24 @@ struct TcRowWriter {   // encoded features of one point -> swizzled row of the A
     {
         *reinterpret_cast<__half*>(aBuf + sw128_offset<TC_TILE>(row, c >> 3) + (c & 7) * 2) = __float2half(v);
     }
+    __device__ __forceinline__ void half(int c, __half v) const
+    {
+        *reinterpret_cast<__half*>(aBuf + sw128_offset<TC_TILE>(row, c >> 3) + (c & 7) * 2) = v;
+    }
+    __device__ __forceinline__ void half2(int c, uint32_t v) const   // channels c, c + 1
+    {
+        if (c & 1) {
+            half(c, __ushort_as_half(static_cast<unsigned short>(v & 0xffffu)));
+            half(c + 1, __ushort_as_half(static_cast<unsigned short>(v >> 16)));
+        } else {
+            *reinterpret_cast<uint32_t*>(aBuf + sw128_offset<TC_TILE>(row, c >> 3) + (c & 7) * 2) = v;
+        }
+    }
 };
 
 // Stage 0: encode the point into the layer-0 operand. Stage L+1: epilogue of layer L. Each stage but the last ends
 // by launching the MMAs of the next layer. Returns false, for the whole warpgroup at once, when a wait timed out.
-template <class Spec, int ST>
+template <class Spec, int ST, bool PLANES>
 __device__ __forceinline__ bool tc_stage(const LaunchArgs& p, TcSlot& sl, uint64_t biasDesc0, uint64_t wDesc0, int row,
                                          int barrierId, bool issuer)
 {
@@ -286,8 +300,12 @@ __device__ __forceinline__ bool tc_stage(const LaunchArgs& p, TcSlot& sl, uint64
 #pragma unroll
         for (int c = 0; c < CIN0 / 8; ++c) *reinterpret_cast<uint4*>(sl.aBuf + sw128_offset<TC_TILE>(row, c)) = make_uint4(0, 0, 0, 0);
         if (sl.gRow < p.numel) {
-            RowReader in{p.input + sl.gRow * p.inS0, p.inS1};
-            encode_point<Spec, 0>(p, in, TcRowWriter{sl.aBuf, row});
+            if constexpr (PLANES) {
+                read_planes_point<Spec, 0>(p, sl.gRow, TcRowWriter{sl.aBuf, row});
+            } else {
+                RowReader in{p.input + sl.gRow * p.inS0, p.inS1};
+                encode_point<Spec, 0>(p, in, TcRowWriter{sl.aBuf, row});
+            }
         }
     } else {
         constexpr int L = ST - 1;
@@ -351,7 +369,7 @@ __device__ __forceinline__ bool tc_stage(const LaunchArgs& p, TcSlot& sl, uint64
 }
 
 // all stages of up to SPW tiles, interleaved stage by stage
-template <class Spec, int ST, int SPW>
+template <class Spec, int ST, int SPW, bool PLANES>
 __device__ __forceinline__ bool tc_run_stages(const LaunchArgs& p, TcSlot (&sl)[SPW], uint64_t biasDesc0, uint64_t wDesc0, int row,
                                               int barrierId, bool issuer)
 {
@@ -359,15 +377,15 @@ __device__ __forceinline__ bool tc_run_stages(const LaunchArgs& p, TcSlot (&sl)[
 #pragma unroll
         for (int j = 0; j < SPW; ++j)
             if (sl[j].active) {   // uniform over the warpgroup
-                if (!tc_stage<Spec, ST>(p, sl[j], biasDesc0, wDesc0, row, barrierId, issuer)) return false;
+                if (!tc_stage<Spec, ST, PLANES>(p, sl[j], biasDesc0, wDesc0, row, barrierId, issuer)) return false;
             }
-        return tc_run_stages<Spec, ST + 1, SPW>(p, sl, biasDesc0, wDesc0, row, barrierId, issuer);
+        return tc_run_stages<Spec, ST + 1, SPW, PLANES>(p, sl, biasDesc0, wDesc0, row, barrierId, issuer);
     } else {
         return true;
     }
 }
 
-template <class Spec>
+template <class Spec, bool PLANES>
 __global__ void __launch_bounds__(TcLayout<Spec>::warpgroups() * 128, 1)
 fused_forward_tc_kernel(const __grid_constant__ LaunchArgs p)
 {
@@ -435,7 +453,7 @@ fused_forward_tc_kernel(const __grid_constant__ LaunchArgs p)
             sl[j].active = i + j < myTiles;
             sl[j].gRow = (firstTile + (i + j) * stride) * TC_TILE + row;
         }
-        ok = tc_run_stages<Spec, 0, SPW>(p, sl, biasDesc0, wDesc0, row, 1 + wg, issuer);
+        ok = tc_run_stages<Spec, 0, SPW, PLANES>(p, sl, biasDesc0, wDesc0, row, 1 + wg, issuer);
     }
     if (!ok) *abortFlag = 1;
     // drain: every warpgroup reaches this point (all waits are bounded), then tensor memory is released
@@ -450,13 +468,14 @@ fused_forward_tc_kernel(const __grid_constant__ LaunchArgs p)
 
 template <class Spec>
 struct TcLaunchers {
-    static cudaError_t inference(const LaunchArgs& a, cudaStream_t s)
+    template <bool PLANES>
+    static cudaError_t run(const LaunchArgs& a, cudaStream_t s)
     {
         using TL = TcLayout<Spec>;
         constexpr int smem = TL::totalBytes();
         constexpr int threads = TL::warpgroups() * 128;
         static bool configured = false;
-        auto k = fused_forward_tc_kernel<Spec>;
+        auto k = fused_forward_tc_kernel<Spec, PLANES>;
         if (!configured) {
             cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
             if (e != cudaSuccess) return e;
@@ -466,6 +485,19 @@ struct TcLaunchers {
         long long blocks = tiles < a.numSMs ? tiles : a.numSMs;
         if (blocks < 1) blocks = 1;
         k<<<static_cast<unsigned>(blocks), threads, smem, s>>>(a);
+        return cudaGetLastError();
+    }
+    static cudaError_t inference(const LaunchArgs& a, cudaStream_t s) { return run<false>(a, s); }
+    static cudaError_t inferencePlanes(const LaunchArgs& a, cudaStream_t s) { return run<true>(a, s); }
+    // level-major encoding pass: blockIdx.y = level (slow), blockIdx.x strides over the points of the chunk
+    static cudaError_t encodePlanes(const LaunchArgs& a, cudaStream_t s)
+    {
+        constexpr int groups = plane_group_count<Spec>();
+        long long bx = (a.numel + 255) / 256;
+        const long long cap = static_cast<long long>(a.numSMs) * 8;
+        if (bx > cap) bx = cap;
+        if (bx < 1) bx = 1;
+        encode_planes_kernel<Spec><<<dim3(static_cast<unsigned>(bx), groups), 256, 0, s>>>(a);
         return cudaGetLastError();
     }
 };

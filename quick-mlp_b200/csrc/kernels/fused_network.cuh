@@ -746,6 +746,14 @@ struct NetworkLaunchers {
             }
             e = forward<0>(a, s);
             break;
+        case KERNEL_ENCODE_PLANES:
+            if constexpr (TcLayout<Spec>::eligible()) e = TcLaunchers<Spec>::encodePlanes(a, s);
+            else e = cudaErrorNotSupported;   // the caller falls back to the fused gather
+            break;
+        case KERNEL_INFERENCE_PLANES:
+            if constexpr (TcLayout<Spec>::eligible()) e = TcLaunchers<Spec>::inferencePlanes(a, s);
+            else e = cudaErrorNotSupported;
+            break;
         case KERNEL_FORWARD: e = forward<1>(a, s); break;
         case KERNEL_FORWARD_LOSS: e = forward<2>(a, s); break;
         case KERNEL_BACKWARD: e = backward(a, s); n = (a.flags & 7) ? 1 : 0; break;

@@ -1,0 +1,153 @@
+// Level-major encoding pass for networks whose grid tables do not fit in L2.
+//
+// When the gather runs inside the fused kernel, every warp walks through all levels of its own points, so at any moment
+// the SMs touch all tables at once: with tables far larger than the 126 MB L2 (BASELINE configuration 5: 12 hashed
+// levels of 2^22 rows) nearly every corner fetch is a random 32-byte DRAM sector. This pass reorders the work instead
+// of the data: the encodings of a chunk of points are computed one level at a time by the whole GPU (blockIdx.y =
+// level, the slow grid dimension), so the table of the level being processed (32 MB in fp16) stays resident in L2 and
+// corner fetches hit it there. The features go to level-major planes ([level][point][F] halfs, coalesced 4/8/16-byte
+// stores); the layer-chain kernel then reads its layer-0 operand from the planes (coalesced) instead of gathering.
+// The chunk is sized so that planes and one table level together stay inside L2.
+//
+// Same arithmetic as the fused gather (grid.cuh; reference: src_cpp/include/qmlp/kernels/encoding_hashgrid.cuh:267-336).
+#pragma once
+#include "fused_network.cuh"
+
+namespace qmlp {
+namespace kernel {
+
+// "groups": one per level of a concatenating grid, one for an adding grid, one for an identity encoding
+template <class Spec, int E>
+struct PlaneGroups {
+    using Enc = typename Spec::template Enc<E>;
+    __host__ __device__ static constexpr int own()
+    {
+        if constexpr (Enc::IS_GRID) return Enc::CONCAT ? Enc::L : 1;
+        else return 1;
+    }
+    __host__ __device__ static constexpr int before()
+    {
+        if constexpr (E == 0) return 0;
+        else return PlaneGroups<Spec, E - 1>::before() + PlaneGroups<Spec, E - 1>::own();
+    }
+};
+template <class Spec>
+__host__ __device__ constexpr int plane_group_count()
+{
+    return PlaneGroups<Spec, Spec::NUM_ENCODINGS - 1>::before() + PlaneGroups<Spec, Spec::NUM_ENCODINGS - 1>::own();
+}
+
+template <int W>
+__device__ __forceinline__ void store_halfs(__half* dst, const float (&v)[W])
+{
+    if constexpr (W == 2) {
+        *reinterpret_cast<__half2*>(dst) = __floats2half2_rn(v[0], v[1]);
+    } else if constexpr (W == 4) {
+        uint2 u;
+        u.x = h2_as_u32(__floats2half2_rn(v[0], v[1]));
+        u.y = h2_as_u32(__floats2half2_rn(v[2], v[3]));
+        *reinterpret_cast<uint2*>(dst) = u;
+    } else if constexpr (W == 8) {
+        uint4 u;
+        u.x = h2_as_u32(__floats2half2_rn(v[0], v[1]));
+        u.y = h2_as_u32(__floats2half2_rn(v[2], v[3]));
+        u.z = h2_as_u32(__floats2half2_rn(v[4], v[5]));
+        u.w = h2_as_u32(__floats2half2_rn(v[6], v[7]));
+        *reinterpret_cast<uint4*>(dst) = u;
+    } else {
+#pragma unroll
+        for (int i = 0; i < W; ++i) dst[i] = __float2half(v[i]);
+    }
+}
+
+// features of group `g` (relative to all groups) for one point -> its plane
+template <class Spec, int E>
+__device__ __forceinline__ void encode_group(const LaunchArgs& p, int g, const RowReader& in, long long local)
+{
+    if constexpr (E < Spec::NUM_ENCODINGS) {
+        using Enc = typename Spec::template Enc<E>;
+        using PG = PlaneGroups<Spec, E>;
+        if (g >= PG::before() + PG::own()) {
+            encode_group<Spec, E + 1>(p, g, in, local);
+            return;
+        }
+        if constexpr (!Enc::IS_GRID) {
+            float v[Enc::N];
+#pragma unroll
+            for (int i = 0; i < Enc::N; ++i) v[i] = in(i + Enc::START);
+            store_halfs<Enc::N>(p.planes + p.planeStride * Enc::OUT_OFF + local * Enc::N, v);
+        } else {
+            const GridP& grid = p.grids[Enc::SLOT];
+            float pos[Enc::D];
+            grid_position<Enc::D, Enc::START>(grid, in, pos);
+            float feat[Enc::F];
+            if constexpr (Enc::CONCAT) {
+                const int l = g - PG::before();
+                grid_level_forward<Enc::D, Enc::F, Enc::HALF_TABLE>(grid, grid.levels[l], pos, feat);
+                store_halfs<Enc::F>(p.planes + p.planeStride * (Enc::OUT_OFF + l * Enc::F) + local * Enc::F, feat);
+            } else {
+#pragma unroll
+                for (int i = 0; i < Enc::F; ++i) feat[i] = 0.f;
+                for (int l = 0; l < Enc::L; ++l) {
+                    float f[Enc::F];
+                    grid_level_forward<Enc::D, Enc::F, Enc::HALF_TABLE>(grid, grid.levels[l], pos, f);
+#pragma unroll
+                    for (int i = 0; i < Enc::F; ++i) feat[i] += f[i];
+                }
+                store_halfs<Enc::F>(p.planes + p.planeStride * Enc::OUT_OFF + local * Enc::F, feat);
+            }
+        }
+    }
+}
+
+template <class Spec>
+__global__ void __launch_bounds__(256) encode_planes_kernel(const __grid_constant__ LaunchArgs p)
+{
+    const int g = blockIdx.y;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < p.numel;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        RowReader in{p.input + i * p.inS0, p.inS1};
+        encode_group<Spec, 0>(p, g, in, i);
+    }
+}
+
+// layer-0 operand row of one point from the planes (Out writes halfs: out.half(channel, value))
+template <class Spec, int E, class Out>
+__device__ __forceinline__ void read_planes_point(const LaunchArgs& p, long long local, const Out& out)
+{
+    if constexpr (E < Spec::NUM_ENCODINGS) {
+        using Enc = typename Spec::template Enc<E>;
+        if constexpr (!Enc::IS_GRID) {
+            const __half* src = p.planes + p.planeStride * Enc::OUT_OFF + local * Enc::N;
+#pragma unroll
+            for (int i = 0; i < Enc::N; ++i) out.half(Enc::OUT_OFF + i, src[i]);
+        } else {
+            constexpr int GROUPS = Enc::CONCAT ? Enc::L : 1;
+#pragma unroll
+            for (int l = 0; l < GROUPS; ++l) {
+                const int c0 = Enc::OUT_OFF + l * Enc::F;
+                const __half* src = p.planes + p.planeStride * c0 + local * Enc::F;
+                if constexpr (Enc::F == 2) {
+                    out.half2(c0, *reinterpret_cast<const uint32_t*>(src));
+                } else if constexpr (Enc::F == 4) {
+                    const uint2 u = *reinterpret_cast<const uint2*>(src);
+                    out.half2(c0, u.x);
+                    out.half2(c0 + 2, u.y);
+                } else if constexpr (Enc::F == 8) {
+                    const uint4 u = *reinterpret_cast<const uint4*>(src);
+                    out.half2(c0, u.x);
+                    out.half2(c0 + 2, u.y);
+                    out.half2(c0 + 4, u.z);
+                    out.half2(c0 + 6, u.w);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < Enc::F; ++i) out.half(c0 + i, src[i]);
+                }
+            }
+        }
+        read_planes_point<Spec, E + 1, Out>(p, local, out);
+    }
+}
+
+} // namespace kernel
+} // namespace qmlp

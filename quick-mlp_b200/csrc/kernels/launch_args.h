@@ -55,6 +55,8 @@ struct LaunchArgs {
     int numGrids;
     int forcePath;                                 // 0: best path for the spec, 1: mma.sync kernels only
     int* status;                                   // device word set to 1 when a kernel gave up on a bounded wait
+    __half* planes;                                // encoded features of a chunk of points, one plane per grid level
+    long long planeStride;                         // points per plane (capacity of the chunk buffer)
     GridP grids[MAX_GRIDS];
 };
 
@@ -68,7 +70,9 @@ enum KernelId {
     KERNEL_ENCODING_FORWARD = 5,
     KERNEL_ENCODING_ADJOINT = 6,
     KERNEL_ACTIVATION_FORWARD = 7,
-    KERNEL_ACTIVATION_ADJOINT = 8
+    KERNEL_ACTIVATION_ADJOINT = 8,
+    KERNEL_ENCODE_PLANES = 9,      // encodings of a chunk of points -> level-major feature planes
+    KERNEL_INFERENCE_PLANES = 10   // layer chain reading the feature planes instead of running the encodings
 };
 
 // arguments of the stand-alone activation kernels
@@ -87,4 +91,4 @@ extern "C" {
 typedef int (*qmlp_spec_launch_fn)(int kernel, const void* args, cudaStream_t stream, int* launches);
 typedef int (*qmlp_spec_abi_fn)(void);
 }
-#define QMLP_SPEC_ABI_VERSION 4
+#define QMLP_SPEC_ABI_VERSION 5

@@ -59,23 +59,24 @@ __device__ __forceinline__ void red_add_v4_f32(float* addr, float a, float b, fl
     asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};\n" :: "l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-// read-only loads that bypass L1 allocation (streamed table rows)
+// read-only table gathers; the rows stay in L1 (evict_last) because the coarse levels' corners are shared by
+// neighbouring points of a tile
 __device__ __forceinline__ uint32_t ldg_nc_u32(const void* p)
 {
     uint32_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.b32 %0, [%1];\n" : "=r"(v) : "l"(p));
+    asm volatile("ld.global.nc.L1::evict_last.b32 %0, [%1];\n" : "=r"(v) : "l"(p));
     return v;
 }
 __device__ __forceinline__ uint2 ldg_nc_u64(const void* p)
 {
     uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.b32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    asm volatile("ld.global.nc.L1::evict_last.v2.b32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "l"(p));
     return v;
 }
 __device__ __forceinline__ uint4 ldg_nc_u128(const void* p)
 {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];\n"
+    asm volatile("ld.global.nc.L1::evict_last.v4.b32 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }

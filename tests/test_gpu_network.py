@@ -115,6 +115,33 @@ def test_tensor_core_paths_agree(name, n):
                          max_violations=0.005)
 
 
+@pytest.mark.parametrize("name", ["config3_small", "config4_small", "config5_small", "grid2d_add_plus_identity"])
+@pytest.mark.parametrize("half_tables", [False, True])
+def test_level_major_encoding_pass(name, half_tables):
+    """Inference through the level-major encoding pass (encodings of a chunk computed one grid level at a time into
+    feature planes, then the layer chain on the planes) equals the fused gather, also across several chunks."""
+    import torch
+    from qmlp import bindings
+    cfg, rng, spec, net, params, tables, acts, t_params, t_tables = _setup(name)
+    n = (1 << 18) + 4321 if name == "config3_small" else 3000       # more than one chunk for one case
+    x = torch.from_numpy(helpers.uniform(42, 8, (n, spec.num_inputs), *rng)).cuda()
+    tabs = [t.half() if (t is not None and half_tables) else t for t in t_tables]
+    try:
+        bindings.QuickMLP.set_kernel_path(2)
+        out_planes = net.inference(x, t_params, tabs)
+        bindings.QuickMLP.set_kernel_path(0)
+        out_fused = net.inference(x, t_params, tabs)
+    finally:
+        bindings.QuickMLP.set_kernel_path(0)
+    assert bindings.QuickMLP.device_status() == 0
+    helpers.assert_close(out_planes.cpu().numpy(), out_fused.cpu().numpy(), f"{name} planes vs fused", rtol=5e-3, atol=1e-3,
+                         max_violations=0.005)
+    m = 2000
+    tabs_np = [t.astype(np.float16).astype(np.float32) if (t is not None and half_tables) else t for t in tables]
+    emu = oracle.network_forward(spec, params, x[-m:].cpu().numpy(), tabs_np, half=True, activations=acts)
+    helpers.assert_close(out_planes[-m:].cpu().numpy(), emu, f"{name} planes vs oracle", max_violations=0.01)
+
+
 def test_inference_half_tables_and_strided_io():
     """fp16 gather table (extension) and non-contiguous input/output views."""
     import torch
