@@ -293,10 +293,21 @@ int qmlp_network_inference(qmlp_network_t* net, const qmlp_tensor_t* input, qmlp
     const bool wantPlanes = !n.planesUnsupported && a.numGrids > 0 && a.numel > 0 &&
                             (path == 2 || (path == 0 && n.gridTableBytes() > (96ll << 20)));
     if (wantPlanes) {
-        const int64_t cap = 1 << 18;
-        if (n.planes == nullptr) {
-            checkCuda(cudaMalloc(&n.planes, static_cast<size_t>(cap) * n.encodedChannels() * 2), "cudaMalloc(feature planes)");
-            n.planeCapacity = cap;
+        // Chunk: as many points as fit in 512 MB of planes, at most 2^22. A level's table is fetched from HBM once per
+        // chunk, so large chunks amortise it; the planes themselves are streamed (written once, read once).
+        const int64_t rowBytes = static_cast<int64_t>(n.encodedChannels()) * 2;
+        int64_t cap = 1 << 16;
+        while (cap < (1 << 22) && cap * 2 * rowBytes <= (512ll << 20)) cap *= 2;
+        const int64_t need = std::min<int64_t>(cap, (a.numel + 65535) / 65536 * 65536);
+        if (n.planeCapacity < need) {
+            if (n.planes) {
+                checkCuda(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)), "cudaStreamSynchronize");
+                checkCuda(cudaFree(n.planes), "cudaFree(feature planes)");
+                n.planes = nullptr;
+                n.planeCapacity = 0;
+            }
+            checkCuda(cudaMalloc(&n.planes, static_cast<size_t>(need * rowBytes)), "cudaMalloc(feature planes)");
+            n.planeCapacity = need;
         }
         auto m = n.module(n.currentHalfMask());
         const long long total = a.numel;

@@ -147,6 +147,39 @@ __device__ __forceinline__ void grid_level_forward(const GridP& g, const GridLev
     GridCell<D> c;
     grid_cell<D>(pos, lv.resolution, c);
     const bool vec = g.vecOk != 0;
+    if constexpr (HALF && (F == 2 || F == 4 || F == 8)) {
+        // fp16 rows stay packed while the loads are in flight (half the registers of the unpacked rows, so more warps
+        // fit on the SM to hide the gather latency); same blend order as below
+        if (vec) {
+            uint32_t raw[1 << D][F / 2];
+#pragma unroll
+            for (int b = 0; b < (1 << D); ++b) {
+                const __half* t = static_cast<const __half*>(g.table) + grid_corner_index<D, F>(c, lv, b);
+                if constexpr (F == 2) {
+                    raw[b][0] = ldg_nc_u32(t);
+                } else if constexpr (F == 4) {
+                    const uint2 u = ldg_nc_u64(t);
+                    raw[b][0] = u.x; raw[b][1] = u.y;
+                } else {
+                    const uint4 u = ldg_nc_u128(t);
+                    raw[b][0] = u.x; raw[b][1] = u.y; raw[b][2] = u.z; raw[b][3] = u.w;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < F; ++i) feat[i] = 0.f;
+#pragma unroll
+            for (int b = 0; b < (1 << D); ++b) {
+                const float w = grid_corner_weight<D>(c, b);
+#pragma unroll
+                for (int i = 0; i < F / 2; ++i) {
+                    const float2 x = __half22float2(u32_as_h2(raw[b][i]));
+                    feat[2 * i] += w * x.x;
+                    feat[2 * i + 1] += w * x.y;
+                }
+            }
+            return;
+        }
+    }
     float rows[1 << D][F];
     // issue every corner load before the blend so they are all in flight together
 #pragma unroll

@@ -100,8 +100,32 @@ __device__ __forceinline__ void encode_group(const LaunchArgs& p, int g, const R
     }
 }
 
+// registers that hold one level's corner rows while its gathers are in flight; decides how many CTAs share an SM
+template <class Spec, int E = 0>
+__host__ __device__ constexpr int plane_row_registers()
+{
+    if constexpr (E >= Spec::NUM_ENCODINGS) {
+        return 0;
+    } else {
+        using Enc = typename Spec::template Enc<E>;
+        int own = 0;
+        if constexpr (Enc::IS_GRID) own = (1 << Enc::D) * ((Enc::HALF_TABLE && Enc::F % 2 == 0) ? Enc::F / 2 : Enc::F);
+        const int rest = plane_row_registers<Spec, E + 1>();
+        return own > rest ? own : rest;
+    }
+}
 template <class Spec>
-__global__ void __launch_bounds__(256) encode_planes_kernel(const __grid_constant__ LaunchArgs p)
+__host__ __device__ constexpr int plane_min_blocks()
+{
+#ifdef QMLP_PLANE_MIN_BLOCKS
+    return QMLP_PLANE_MIN_BLOCKS;
+#else
+    return plane_row_registers<Spec>() <= 32 ? 4 : (plane_row_registers<Spec>() <= 48 ? 3 : 2);
+#endif
+}
+
+template <class Spec>
+__global__ void __launch_bounds__(256, plane_min_blocks<Spec>()) encode_planes_kernel(const __grid_constant__ LaunchArgs p)
 {
     const int g = blockIdx.y;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < p.numel;

@@ -123,7 +123,7 @@ def test_level_major_encoding_pass(name, half_tables):
     import torch
     from qmlp import bindings
     cfg, rng, spec, net, params, tables, acts, t_params, t_tables = _setup(name)
-    n = (1 << 18) + 4321 if name == "config3_small" else 3000       # more than one chunk for one case
+    n = (1 << 22) + 4321 if name == "config3_small" else 3000       # more than one chunk (2^22 points) for one case
     x = torch.from_numpy(helpers.uniform(42, 8, (n, spec.num_inputs), *rng)).cuda()
     tabs = [t.half() if (t is not None and half_tables) else t for t in t_tables]
     try:
