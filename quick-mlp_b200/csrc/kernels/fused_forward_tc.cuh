@@ -5,7 +5,8 @@
 // machine mapping:
 //   * one persistent CTA per SM; all weight matrices are staged once in shared memory in the K-major, 128-byte
 //     swizzled operand layout the tensor core reads through a shared-memory descriptor;
-//   * the CTA consists of up to four warpgroups of 128 threads. A warpgroup owns one or two tile slots; a slot is one
+//   * the CTA consists of 1, 2, 3, 4 or 8 warpgroups of 128 threads (as many as shared and tensor memory allow for
+//     the spec's widths). A warpgroup owns one or two tile slots; a slot is one
 //     tile of 128 points in flight: an activation operand buffer in shared memory plus an fp32 accumulator in tensor
 //     memory. One thread = one point = one TMEM lane;
 //   * per layer the warpgroup writes the rows of the A operand, synchronises on a named barrier, and one of its threads
@@ -177,10 +178,17 @@ struct TcLayout {
 #endif
     // 8 warpgroups (1024 threads, 64 registers each) with one slot each, or up to 4 warpgroups (128 registers) that
     // alternate between two slots when shared and tensor memory allow
-    __host__ __device__ static constexpr int warpgroups() { return (QMLP_TC_MAX_WARPGROUPS >= 8 && fits(8)) ? 8 : fits(4) ? 4 : fits(2) ? 2 : 1; }
+    __host__ __device__ static constexpr int warpgroups() { return (QMLP_TC_MAX_WARPGROUPS >= 8 && fits(8)) ? 8 : fits(4) ? 4 : fits(3) ? 3 : fits(2) ? 2 : 1; }
     __host__ __device__ static constexpr int slotsPerWarpgroup() { return warpgroups() < 8 && fits(2 * warpgroups()) ? 2 : 1; }
     __host__ __device__ static constexpr int loadWidth() { return warpgroups() == 8 ? 32 : 64; }
     __host__ __device__ static constexpr int slots() { return warpgroups() * slotsPerWarpgroup(); }
+    // tensor-memory allocation: a power of two >= 32 columns
+    __host__ __device__ static constexpr int tmemCols()
+    {
+        int c = 32;
+        while (c < slots() * accCols()) c *= 2;
+        return c;
+    }
     __host__ __device__ static constexpr bool eligible()
     {
         return maxCout() <= 128 && maxCin() <= 128 && fits(1);
@@ -414,7 +422,7 @@ fused_forward_tc_kernel(const __grid_constant__ LaunchArgs p)
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
-        tmem_alloc(smem_u32(tmemSlot), SLOTS * TL::accCols());
+        tmem_alloc(smem_u32(tmemSlot), TL::tmemCols());
         tmem_relinquish();
     }
     fence_proxy_async();   // staged weights -> visible to the tensor core
@@ -461,7 +469,7 @@ fused_forward_tc_kernel(const __grid_constant__ LaunchArgs p)
     __syncthreads();
     if (warp == 0) {
         tc_fence_after();
-        tmem_dealloc(tmemBase, SLOTS * TL::accCols());
+        tmem_dealloc(tmemBase, TL::tmemCols());
     }
     if (threadIdx.x == 0 && *abortFlag && p.status != nullptr) atomicExch(p.status, 1);
 }
