@@ -82,9 +82,10 @@ QMLP_API int qmlp_set_kernel_include_dir(const char* dir);
 
 /* Kernel family used for fused inference: 0 = the best one instantiated for the spec (tcgen05 tensor-core kernel when
  * the layer widths allow it; a level-major encoding pass in front of it when the grid tables are much larger than L2,
- * which makes the network keep a 2^18-point feature buffer from its first such call until it is destroyed),
- * 1 = the mma.sync kernels only, 2 = the level-major pass for every grid network. Takes the place of the reference's per-kernel tuning
- * options (overwrite_blocksize_*, skew_shared_memory; src_cpp/src/fused_network.cpp:45-69). */
+ * which makes the network keep a feature buffer of up to 2^22 points and 512 MB from its first such call until it is
+ * destroyed), 1 = the mma.sync kernels only, 2 = the level-major pass for every grid network. Takes the place of the
+ * reference's per-kernel tuning options (overwrite_blocksize_*, skew_shared_memory;
+ * src_cpp/src/fused_network.cpp:45-69). */
 QMLP_API int qmlp_set_kernel_path(int path);
 /* Synchronises the current device and returns (then clears) its kernel status word: 0 = every kernel ran to completion,
  * 1 = a kernel gave up on a bounded on-chip wait and its results are invalid. The reference has no counterpart (its
@@ -120,6 +121,16 @@ QMLP_API int qmlp_network_initialize_parameters_host(qmlp_network_t* net, uint64
 /* FusedNetwork::inference, src_cpp/src/fused_network.cpp:507-551 */
 QMLP_API int qmlp_network_inference(qmlp_network_t* net, const qmlp_tensor_t* input, qmlp_tensor_t* output,
                                     qmlp_stream_t stream);
+/* Inference from and to HOST memory. The reference has no such call: a host caller of it uploads the whole batch,
+ * runs FusedNetwork::inference (src_cpp/src/fused_network.cpp:507-551) and downloads the whole result, three serial
+ * steps. Here the batch is cut into chunks that move through upload -> kernel -> download on three streams, so the two
+ * directions of the host link and the kernel run concurrently. host_input is (num_points, channels_in) and host_output
+ * (num_points, channels_out), row-major fp32; both should be page-locked (with pageable memory the copies serialise).
+ * chunk_points 0 picks a chunk of about an eighth of the batch (2^16 ... 2^20 points). The kernels run on `stream`;
+ * when the call returns, everything is queued and `stream` completes after the last download. Device staging buffers
+ * (3 x chunk x (channels_in + channels_out) x 4 bytes) are allocated at the first call and kept with the network. */
+QMLP_API int qmlp_network_inference_host(qmlp_network_t* net, const float* host_input, float* host_output,
+                                         int64_t num_points, int64_t chunk_points, qmlp_stream_t stream);
 /* FusedNetwork::forwardMemory, src_cpp/src/fused_network.cpp:674-689 */
 QMLP_API int qmlp_network_forward_memory(qmlp_network_t* net, int64_t num_elements, int adjoint_flags, size_t* bytes);
 /* FusedNetwork::forward, src_cpp/src/fused_network.cpp:691-736 */

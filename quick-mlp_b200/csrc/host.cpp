@@ -466,6 +466,58 @@ Network::Network(const Json& cfg, const std::string& parent)
 Network::~Network()
 {
     if (planes != nullptr) cudaFree(planes);
+    hostPipeline.release();
+}
+
+static void pipelineCheck(cudaError_t e, const char* what)
+{
+    if (e != cudaSuccess) throw cuda_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+void HostPipeline::reserve(int64_t points, int channelsIn, int channelsOut)
+{
+    if (copyIn == nullptr) {
+        pipelineCheck(cudaStreamCreateWithFlags(&copyIn, cudaStreamNonBlocking), "cudaStreamCreate");
+        pipelineCheck(cudaStreamCreateWithFlags(&copyOut, cudaStreamNonBlocking), "cudaStreamCreate");
+        pipelineCheck(cudaEventCreateWithFlags(&start, cudaEventDisableTiming), "cudaEventCreate");
+        for (int s = 0; s < SLOTS; ++s) {
+            pipelineCheck(cudaEventCreateWithFlags(&uploaded[s], cudaEventDisableTiming), "cudaEventCreate");
+            pipelineCheck(cudaEventCreateWithFlags(&computed[s], cudaEventDisableTiming), "cudaEventCreate");
+            pipelineCheck(cudaEventCreateWithFlags(&downloaded[s], cudaEventDisableTiming), "cudaEventCreate");
+        }
+    }
+    if (points <= capacity) return;
+    // cudaFree waits for the device, so no earlier call still uses the old slots
+    for (int s = 0; s < SLOTS; ++s) {
+        if (in[s]) cudaFree(in[s]);
+        if (out[s]) cudaFree(out[s]);
+        in[s] = out[s] = nullptr;
+    }
+    capacity = 0;
+    for (int s = 0; s < SLOTS; ++s) {
+        pipelineCheck(cudaMalloc(&in[s], static_cast<size_t>(points) * channelsIn * sizeof(float)), "cudaMalloc(upload slot)");
+        pipelineCheck(cudaMalloc(&out[s], static_cast<size_t>(points) * channelsOut * sizeof(float)), "cudaMalloc(download slot)");
+    }
+    capacity = points;
+}
+
+void HostPipeline::release()
+{
+    for (int s = 0; s < SLOTS; ++s) {
+        if (in[s]) cudaFree(in[s]);
+        if (out[s]) cudaFree(out[s]);
+        if (uploaded[s]) cudaEventDestroy(uploaded[s]);
+        if (computed[s]) cudaEventDestroy(computed[s]);
+        if (downloaded[s]) cudaEventDestroy(downloaded[s]);
+        in[s] = out[s] = nullptr;
+        uploaded[s] = computed[s] = downloaded[s] = nullptr;
+    }
+    if (start) cudaEventDestroy(start);
+    if (copyIn) cudaStreamDestroy(copyIn);
+    if (copyOut) cudaStreamDestroy(copyOut);
+    start = nullptr;
+    copyIn = copyOut = nullptr;
+    capacity = 0;
 }
 
 int64_t Network::gridTableBytes() const

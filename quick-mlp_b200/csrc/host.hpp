@@ -180,6 +180,21 @@ struct LayerSpec {
     int64_t weightsStart = 0, biasStart = -1;
 };
 
+// Device staging of the host-memory inference entry point: three chunk slots (input + output), an upload and a
+// download stream, and the events that chain upload -> kernel -> download per slot. Created at the first such call on a
+// network, grown when a larger chunk is asked for, released with the network.
+struct HostPipeline {
+    static constexpr int SLOTS = 3;
+    cudaStream_t copyIn = nullptr, copyOut = nullptr;
+    cudaEvent_t start = nullptr;
+    cudaEvent_t uploaded[SLOTS] = {}, computed[SLOTS] = {}, downloaded[SLOTS] = {};
+    float* in[SLOTS] = {};
+    float* out[SLOTS] = {};
+    int64_t capacity = 0;   // points per slot
+    void reserve(int64_t points, int channelsIn, int channelsOut);
+    void release();
+};
+
 class Network {
 public:
     Network(const Json& cfg, const std::string& parent);
@@ -209,6 +224,7 @@ public:
     void* planes = nullptr;
     int64_t planeCapacity = 0;        // points per chunk
     bool planesUnsupported = false;   // the spec has no instantiation of the plane kernels
+    HostPipeline hostPipeline;
 
     BoundTensor paramInference, paramGradients;
     std::vector<qmlp_encoding*> encodingHandles; // owned wrappers handed out through the C ABI

@@ -69,6 +69,7 @@ SIGNATURES = {
     "qmlp_network_initialize_parameters": (C.c_int, [_P, C.c_uint64]),
     "qmlp_network_initialize_parameters_host": (C.c_int, [_P, C.c_uint64, _P]),
     "qmlp_network_inference": (C.c_int, [_P, _TP, _TP, _P]),
+    "qmlp_network_inference_host": (C.c_int, [_P, _P, _P, C.c_int64, C.c_int64, _P]),
     "qmlp_network_forward_memory": (C.c_int, [_P, C.c_int64, C.c_int, C.POINTER(C.c_size_t)]),
     "qmlp_network_forward": (C.c_int, [_P, _TP, _TP, _P, _P]),
     "qmlp_network_forward_static_scratch": (C.c_int, [_P, _TP, _TP, _P]),

@@ -356,6 +356,25 @@ class Network:
             check(lib().qmlp_network_inference(self._h, wrap(input), wrap(output), current_stream()))
             return output
 
+    def inference_host(self, input: torch.Tensor, network_parameters: torch.Tensor,
+                       encoding_parameters: Sequence[Optional[torch.Tensor]] = (),
+                       output: Optional[torch.Tensor] = None, chunk_points: int = 0) -> torch.Tensor:
+        """Inference of a batch that lives in host memory: `input` is a contiguous fp32 CPU tensor (page-locked for the
+        copies to overlap), the result is a CPU tensor (`output` if given, else a new page-locked one). Parameters are
+        device tensors as in `inference`. Uploads, kernels and downloads of successive chunks overlap
+        (qmlp_network_inference_host); the result is complete once the current CUDA stream is."""
+        assert input.device.type == "cpu" and input.dtype == torch.float32 and input.is_contiguous()
+        with self._mutex:
+            n = input.shape[0]
+            if output is None:
+                output = torch.empty((n, self.channels_out()), dtype=torch.float32, pin_memory=True)
+            assert output.device.type == "cpu" and output.dtype == torch.float32 and output.is_contiguous()
+            assert tuple(output.shape) == (n, self.channels_out()) and input.shape[1] == self.channels_in()
+            self._bind(self._half(network_parameters), encoding_parameters)
+            check(lib().qmlp_network_inference_host(self._h, input.data_ptr(), output.data_ptr(), n, int(chunk_points),
+                                                    current_stream()))
+            return output
+
     def forward(self, input: torch.Tensor, network_parameters: torch.Tensor,
                 encoding_parameters: Sequence[Optional[torch.Tensor]] = ()) -> torch.Tensor:
         flags = 0

@@ -142,6 +142,32 @@ def test_level_major_encoding_pass(name, half_tables):
     helpers.assert_close(out_planes[-m:].cpu().numpy(), emu, f"{name} planes vs oracle", max_violations=0.01)
 
 
+@pytest.mark.parametrize("name,n,chunk", [("config2", 100_003, 0), ("config2", 5000, 1024), ("config3_small", 70_001, 4096),
+                                          ("config1", 17, 0), ("config1", 0, 0)])
+def test_inference_from_host_memory(name, n, chunk):
+    """The chunk-pipelined host-memory entry point returns exactly what the device-tensor call returns, for ragged
+    last chunks, batches smaller than a chunk, an empty batch, and when called twice in a row on the same buffers."""
+    import torch
+    cfg, rng, spec, net, params, tables, acts, t_params, t_tables = _setup(name)
+    x = torch.from_numpy(helpers.uniform(42, 9, (n, spec.num_inputs), *rng))
+    hx = x.pin_memory()
+    ref = net.inference(x.cuda(), t_params, t_tables).cpu()
+    out = net.inference_host(hx, t_params, t_tables, chunk_points=chunk)
+    torch.cuda.current_stream().synchronize()
+    assert out.shape == ref.shape
+    assert torch.equal(out, ref)
+    out.zero_()
+    out2 = net.inference_host(hx, t_params, t_tables, output=out, chunk_points=chunk)
+    torch.cuda.current_stream().synchronize()
+    assert out2 is out and torch.equal(out, ref)
+    assert bindings_status() == 0
+
+
+def bindings_status():
+    from qmlp import bindings
+    return bindings.QuickMLP.device_status()
+
+
 def test_inference_half_tables_and_strided_io():
     """fp16 gather table (extension) and non-contiguous input/output views."""
     import torch
