@@ -109,6 +109,45 @@ void launchNet(Network& n, int kernelId, const kernel::LaunchArgs& a, qmlp_strea
     n.launchCount += launches;
 }
 
+// Backward launch. With `planes` (n32 x encoded channels halfs) and table gradients but no input gradients requested,
+// the scatter of the table gradients can run as its own kernel (kernels/grid_planes.cuh) after the backward kernel.
+// Both ways are bound by the L2 reduction rate (one 32-byte sector per clock and slice). The separate kernel merges
+// neighbouring rows of two fp32 features into one 16-byte reduction (a quarter fewer L2 operations; config 3: 951 ->
+// 848 us); with wider rows nothing can be merged and the fused scatter, which hides under the backward kernel's MMA
+// phases, is faster (config 4: 1627 us fused, 2058 us split). Hence: split only if every grid has two features.
+void launchBackward(Network& n, kernel::LaunchArgs& a, __half* planes, int64_t n32, qmlp_stream_t stream)
+{
+    bool gridGrad = false;
+    for (int i = 0; i < a.numGrids; ++i) gridGrad = gridGrad || a.grids[i].grad != nullptr;
+    for (int i = 0; i < n.numEncodings(); ++i)
+        if (auto* g = dynamic_cast<EncodingHashGrid*>(n.encoding(i).get())) gridGrad = gridGrad && g->features() == 2;
+    const bool split = planes != nullptr && gridGrad && (a.flags & kernel::FLAG_GRAD_ENCODINGS) != 0 &&
+                       (a.flags & kernel::FLAG_GRAD_INPUT) == 0 && Library::instance().kernelPath != 1;
+    if (split) {
+        a.flags |= kernel::FLAG_SPLIT_SCATTER;
+        a.planes = planes;
+        a.planeStride = n32;
+    }
+    launchNet(n, kernel::KERNEL_BACKWARD, a, stream);
+    if (split) launchNet(n, kernel::KERNEL_SCATTER_PLANES, a, stream);
+}
+
+// layout of the adjoint scratch: [delta of every layer, if weight gradients | adjoint feature planes, if table
+// gradients], the second part 256-byte aligned
+size_t adjointDeltaBytes(const Network& n, int64_t n32, int flags)
+{
+    return (flags & QMLP_GRADIENTS_NETWORK_WEIGHTS) ? static_cast<size_t>(n32) * n.deltaHalfsPerPoint() * 2 : 0;
+}
+size_t adjointPlaneBytes(const Network& n, int64_t n32, int flags)
+{
+    bool anyGrid = false;
+    for (int i = 0; i < n.numEncodings(); ++i) anyGrid = anyGrid || n.encoding(i)->hasParameters();
+    // also reserved when input gradients are requested on top (the planes are not used then), so that scratch sized
+    // for a set of flags is large enough for every subset of it
+    const bool wanted = anyGrid && (flags & QMLP_GRADIENTS_INPUT_ENCODINGS) != 0;
+    return wanted ? static_cast<size_t>(n32) * n.encodedChannels() * 2 : 0;
+}
+
 } // namespace
 
 namespace qmlp {
@@ -443,9 +482,12 @@ int qmlp_network_zero_gradients(qmlp_network_t* net, qmlp_stream_t stream)
 int qmlp_network_adjoint_memory(qmlp_network_t* net, int64_t num_elements, int adjoint_flags, size_t* bytes)
 {
     QMLP_TRY
-    // delta of every layer, fp16, only needed for the weight gradients (src_cpp/src/fused_network.cpp:997-1002)
+    // delta of every layer, fp16, only needed for the weight gradients (src_cpp/src/fused_network.cpp:997-1002), and the
+    // adjoint feature planes of the level-major table-gradient scatter
     const int64_t n32 = (num_elements + 31) / 32 * 32;
-    *bytes = (adjoint_flags & QMLP_GRADIENTS_NETWORK_WEIGHTS) ? static_cast<size_t>(n32) * net->impl->deltaHalfsPerPoint() * 2 : 0;
+    const size_t planes = adjointPlaneBytes(*net->impl, n32, adjoint_flags);
+    const size_t delta = adjointDeltaBytes(*net->impl, n32, adjoint_flags);
+    *bytes = planes ? (delta + 255) / 256 * 256 + planes : delta;
     QMLP_CATCH
 }
 
@@ -474,6 +516,7 @@ int qmlp_network_adjoint(qmlp_network_t* net, const qmlp_tensor_t* input, const 
         if (!n.paramGradients.defined()) throw std::runtime_error("Weight gradients requested, but no gradient tensor is bound (setNetworkParameter(..., GRADIENTS))");
         if (!tmp_adjoint && numel > 0) throw std::runtime_error("tmpMemoryAdjoint is null");
     }
+    if (tmp_adjoint && (reinterpret_cast<uintptr_t>(tmp_adjoint) & 15) != 0) throw std::runtime_error("adjoint scratch memory must be 16-byte aligned");
     kernel::LaunchArgs a;
     fillCommon(n, a, input);
     a.adjOutput = static_cast<const float*>(adj_output->data);
@@ -488,7 +531,11 @@ int qmlp_network_adjoint(qmlp_network_t* net, const qmlp_tensor_t* input, const 
     a.adjTmp = static_cast<__half*>(tmp_adjoint);
     a.flags = (gIn ? kernel::FLAG_GRAD_INPUT : 0) | (gW ? kernel::FLAG_GRAD_WEIGHTS : 0) | (gE ? kernel::FLAG_GRAD_ENCODINGS : 0);
     if (a.flags == 0) return QMLP_OK;
-    launchNet(n, kernel::KERNEL_BACKWARD, a, stream);
+    const int64_t n32 = (numel + 31) / 32 * 32;
+    __half* planes = nullptr;   // a caller that passes no adjoint scratch gets the fused scatter
+    if (tmp_adjoint && adjointPlaneBytes(n, n32, adjoint_flags) > 0)
+        planes = reinterpret_cast<__half*>(static_cast<unsigned char*>(tmp_adjoint) + (adjointDeltaBytes(n, n32, adjoint_flags) + 255) / 256 * 256);
+    launchBackward(n, a, planes, n32, stream);
     if (gW) launchNet(n, kernel::KERNEL_WGRAD, a, stream);
     QMLP_CATCH
 }
@@ -773,6 +820,8 @@ int qmlp_trainer_workspace_bytes(qmlp_trainer_t* tr, int64_t num_elements, size_
     size_t b = static_cast<size_t>(n32) * (n.stashHalfsPerPoint() + n.deltaHalfsPerPoint()) * 2;
     b = (b + 255) / 256 * 256;
     b += static_cast<size_t>(n32) * n.channelsOut() * 4; // dLoss/dOut
+    b = (b + 255) / 256 * 256;
+    b += adjointPlaneBytes(n, n32, QMLP_GRADIENTS_NETWORK_WEIGHTS | QMLP_GRADIENTS_INPUT_ENCODINGS); // adjoint feature planes
     *bytes = b;
     QMLP_CATCH
 }
@@ -857,7 +906,9 @@ int qmlp_trainer_gradients(qmlp_trainer_t* tr, const qmlp_tensor_t* input, const
     bool anyGrid = false;
     for (int i = 0; i < n.numEncodings(); ++i) anyGrid = anyGrid || n.encoding(i)->hasParameters();
     a.flags = kernel::FLAG_GRAD_WEIGHTS | (anyGrid ? kernel::FLAG_GRAD_ENCODINGS : 0);
-    launchNet(n, kernel::KERNEL_BACKWARD, a, stream);
+    size_t pb = b + static_cast<size_t>(n32) * n.channelsOut() * 4;
+    pb = (pb + 255) / 256 * 256;
+    launchBackward(n, a, anyGrid ? reinterpret_cast<__half*>(ws + pb) : nullptr, n32, stream);
     launchNet(n, kernel::KERNEL_WGRAD, a, stream);
     QMLP_CATCH
 }

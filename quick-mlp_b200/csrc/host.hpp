@@ -159,6 +159,7 @@ public:
     void setParameter(const qmlp_tensor_t* t, int usage) override;
     void fillGrid(kernel::GridP& g) const override;
     const std::vector<GridLevel>& levelTable() const { return table_; }
+    int features() const { return features_; }
 
 private:
     int start_, dim_, levels_, features_, log2Hashmap_, hashmapSize_, minRes_, maxRes_;

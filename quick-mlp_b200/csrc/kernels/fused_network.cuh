@@ -354,7 +354,45 @@ __device__ __forceinline__ void encode_adjoint_point(const LaunchArgs& p, const 
     }
 }
 
-// FLAGS: FLAG_GRAD_INPUT | FLAG_GRAD_WEIGHTS | FLAG_GRAD_ENCODINGS
+// Adjoint of the grid features of one point -> level-major planes (one plane per grid level of a concatenating grid,
+// one per adding grid; plane of channel c0 = planes + planeStride * c0, F halfs per point): what
+// scatter_planes_kernel consumes. `row` is the point's row of adjoint features in the warp's shared tile.
+template <class Spec, int E>
+__device__ __forceinline__ void write_adjoint_planes(const LaunchArgs& p, long long point, const __half* row)
+{
+    if constexpr (E < Spec::NUM_ENCODINGS) {
+        using Enc = typename Spec::template Enc<E>;
+        if constexpr (Enc::IS_GRID) {
+            constexpr int GROUPS = Enc::CONCAT ? Enc::L : 1;
+#pragma unroll
+            for (int l = 0; l < GROUPS; ++l) {
+                constexpr int F = Enc::F;
+                const int c0 = Enc::OUT_OFF + l * F;
+                __half* dst = p.planes + p.planeStride * c0 + point * F;
+                if constexpr (F % 2 == 0) {
+                    uint32_t w[F / 2];
+#pragma unroll
+                    for (int i = 0; i < F / 2; ++i)
+                        w[i] = static_cast<uint32_t>(__half_as_ushort(row[c0 + 2 * i])) |
+                               (static_cast<uint32_t>(__half_as_ushort(row[c0 + 2 * i + 1])) << 16);
+                    if constexpr (F == 2) *reinterpret_cast<uint32_t*>(dst) = w[0];
+                    else if constexpr (F == 4) *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+                    else if constexpr (F == 8) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                    else {
+#pragma unroll
+                        for (int i = 0; i < F / 2; ++i) reinterpret_cast<uint32_t*>(dst)[i] = w[i];
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < F; ++i) dst[i] = row[c0 + i];
+                }
+            }
+        }
+        write_adjoint_planes<Spec, E + 1>(p, point, row);
+    }
+}
+
+// FLAGS: FLAG_GRAD_INPUT | FLAG_GRAD_WEIGHTS | FLAG_GRAD_ENCODINGS [| FLAG_SPLIT_SCATTER]
 template <class Spec, int L, int FLAGS>
 __device__ __forceinline__ void backward_layers(const LaunchArgs& p, const __half* sW,
                                                 uint32_t (&adj)[MT][Spec::COUT[L] / 16][4], long long rowBase,
@@ -439,10 +477,14 @@ __device__ __forceinline__ void backward_layers(const LaunchArgs& p, const __hal
             __syncwarp();
             const long long myRow = rowBase + lane;
             if (myRow < p.numel) {
-                RowReader in{p.input + myRow * p.inS0, p.inS1};
-                float* adjInRow = (FLAGS & FLAG_GRAD_INPUT) ? p.adjInput + myRow * p.aiS0 : nullptr;
-                encode_adjoint_point<Spec, 0, (FLAGS & FLAG_GRAD_INPUT) != 0, (FLAGS & FLAG_GRAD_ENCODINGS) != 0>(
-                    p, in, HalfRowReader{tile + lane * TS}, adjInRow, p.aiS1);
+                if constexpr ((FLAGS & FLAG_SPLIT_SCATTER) != 0) {
+                    write_adjoint_planes<Spec, 0>(p, myRow, tile + lane * TS);
+                } else {
+                    RowReader in{p.input + myRow * p.inS0, p.inS1};
+                    float* adjInRow = (FLAGS & FLAG_GRAD_INPUT) ? p.adjInput + myRow * p.aiS0 : nullptr;
+                    encode_adjoint_point<Spec, 0, (FLAGS & FLAG_GRAD_INPUT) != 0, (FLAGS & FLAG_GRAD_ENCODINGS) != 0>(
+                        p, in, HalfRowReader{tile + lane * TS}, adjInRow, p.aiS1);
+                }
             }
             __syncwarp();
         }
@@ -644,6 +686,7 @@ wgrad_kernel(const __grid_constant__ LaunchArgs p)
 // ---- host-side launchers (compiled into each instantiation) -------------------------------------------------------
 template <class Spec> struct TcLayout;     // fused_forward_tc.cuh
 template <class Spec> struct TcLaunchers;
+template <class Spec> struct PlaneLaunchers;
 
 template <class Spec>
 struct NetworkLaunchers {
@@ -703,6 +746,11 @@ struct NetworkLaunchers {
 
     static cudaError_t backward(const LaunchArgs& a, cudaStream_t s)
     {
+        if ((a.flags & FLAG_SPLIT_SCATTER) != 0) {
+            if ((a.flags & 7) == 4) return backwardT<4 | FLAG_SPLIT_SCATTER>(a, s);
+            if ((a.flags & 7) == 6) return backwardT<6 | FLAG_SPLIT_SCATTER>(a, s);
+            return cudaErrorInvalidValue;
+        }
         switch (a.flags & 7) {
         case 0: return cudaSuccess;
         case 1: return backwardT<1>(a, s);
@@ -758,6 +806,7 @@ struct NetworkLaunchers {
         case KERNEL_FORWARD_LOSS: e = forward<2>(a, s); break;
         case KERNEL_BACKWARD: e = backward(a, s); n = (a.flags & 7) ? 1 : 0; break;
         case KERNEL_WGRAD: e = wgrad(a, s); break;
+        case KERNEL_SCATTER_PLANES: e = PlaneLaunchers<Spec>::scatter(a, s); break;
         default: break;
         }
         if (launches) *launches = (e == cudaSuccess) ? n : 0;

@@ -233,5 +233,48 @@ __device__ __forceinline__ void grid_level_adjoint(const GridP& g, const GridLev
     }
 }
 
+// Table gradient of one level with corner pairs merged (same sums as grid_level_adjoint<.., true, false>).
+// The two corners that differ in the pairing dimension are neighbouring rows whenever the cell coordinate in that
+// dimension is even: the hash multiplies dimension 0 by 1, so its low bit survives the xor (hashed levels: dimension
+// 0); dense levels store the last coordinate fastest (dimension D-1). Two neighbouring rows of two fp32 features are
+// one aligned 16-byte vector, i.e. one L2 reduction instead of two; at the upper border both corners are the same row
+// and their weights are added first.
+template <int D, int F>
+__device__ __forceinline__ void grid_level_scatter_paired(const GridP& g, const GridLevelP& lv, const float (&pos)[D],
+                                                          const float (&adjF)[F])
+{
+    GridCell<D> c;
+    grid_cell<D>(pos, lv.resolution, c);
+    const bool vec = g.vecOk != 0;
+    if constexpr (F == 2) {
+        if (vec) {
+            const int pd = lv.hashed ? 0 : D - 1;
+#pragma unroll
+            for (int h = 0; h < (1 << (D - 1)); ++h) {
+                const int b0 = pd == 0 ? (h << 1) : h;
+                const int b1 = b0 | (1 << pd);
+                const unsigned int eA = grid_corner_index<D, F>(c, lv, b0), eB = grid_corner_index<D, F>(c, lv, b1);
+                const float wA = grid_corner_weight<D>(c, b0), wB = grid_corner_weight<D>(c, b1);
+                float* pa = g.grad + eA;
+                float* pb = g.grad + eB;
+                if (eA == eB) {
+                    red_add_v2_f32(pa, (wA + wB) * adjF[0], (wA + wB) * adjF[1]);
+                } else if (eB == eA + 2 && (reinterpret_cast<uintptr_t>(pa) & 15) == 0) {
+                    red_add_v4_f32(pa, wA * adjF[0], wA * adjF[1], wB * adjF[0], wB * adjF[1]);
+                } else if (eA == eB + 2 && (reinterpret_cast<uintptr_t>(pb) & 15) == 0) {
+                    red_add_v4_f32(pb, wB * adjF[0], wB * adjF[1], wA * adjF[0], wA * adjF[1]);
+                } else {
+                    red_add_v2_f32(pa, wA * adjF[0], wA * adjF[1]);
+                    red_add_v2_f32(pb, wB * adjF[0], wB * adjF[1]);
+                }
+            }
+            return;
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < (1 << D); ++b)
+        grid_scatter_row<F>(g.grad, grid_corner_index<D, F>(c, lv, b), vec, grid_corner_weight<D>(c, b), adjF);
+}
+
 } // namespace kernel
 } // namespace qmlp

@@ -135,6 +135,105 @@ __global__ void __launch_bounds__(256, plane_min_blocks<Spec>()) encode_planes_k
     }
 }
 
+// ---- level-major scatter of the table gradients --------------------------------------------------------------------
+// Counterpart of the encoding pass for the backward direction: the backward kernel leaves the adjoint of every grid
+// feature in the planes (write_adjoint_planes), and this kernel turns them into table gradients: light threads, many
+// CTAs per SM, nothing but coalesced plane reads and reductions (the backward kernel itself runs 16 warps per SM at 128
+// registers and alternates between MMA and scatter phases). A "group" is one level of one grid.
+template <class Spec, int E>
+struct ScatterGroups {
+    using Enc = typename Spec::template Enc<E>;
+    __host__ __device__ static constexpr int own()
+    {
+        if constexpr (Enc::IS_GRID) return Enc::L;
+        else return 0;
+    }
+    __host__ __device__ static constexpr int before()
+    {
+        if constexpr (E == 0) return 0;
+        else return ScatterGroups<Spec, E - 1>::before() + ScatterGroups<Spec, E - 1>::own();
+    }
+};
+template <class Spec>
+__host__ __device__ constexpr int scatter_group_count()
+{
+    return ScatterGroups<Spec, Spec::NUM_ENCODINGS - 1>::before() + ScatterGroups<Spec, Spec::NUM_ENCODINGS - 1>::own();
+}
+
+template <class Spec, int E>
+__device__ __forceinline__ void scatter_group(const LaunchArgs& p, int g, const RowReader& in, long long point)
+{
+    if constexpr (E < Spec::NUM_ENCODINGS) {
+        using Enc = typename Spec::template Enc<E>;
+        using SG = ScatterGroups<Spec, E>;
+        if (g >= SG::before() + SG::own()) {
+            scatter_group<Spec, E + 1>(p, g, in, point);
+            return;
+        }
+        if constexpr (Enc::IS_GRID) {
+            const GridP& grid = p.grids[Enc::SLOT];
+            if (grid.grad == nullptr) return;
+            const int l = g - SG::before();
+            const int c0 = Enc::OUT_OFF + (Enc::CONCAT ? l * Enc::F : 0);
+            const __half* src = p.planes + p.planeStride * c0 + point * Enc::F;
+            float adjF[Enc::F];
+            if constexpr (Enc::F == 2) {
+                const float2 x = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(src)));
+                adjF[0] = x.x; adjF[1] = x.y;
+            } else if constexpr (Enc::F == 4) {
+                const uint2 u = *reinterpret_cast<const uint2*>(src);
+                const float2 x = __half22float2(u32_as_h2(u.x)), y = __half22float2(u32_as_h2(u.y));
+                adjF[0] = x.x; adjF[1] = x.y; adjF[2] = y.x; adjF[3] = y.y;
+            } else {
+#pragma unroll
+                for (int i = 0; i < Enc::F; ++i) adjF[i] = __half2float(src[i]);
+            }
+            float pos[Enc::D];
+            grid_position<Enc::D, Enc::START>(grid, in, pos);
+            grid_level_scatter_paired<Enc::D, Enc::F>(grid, grid.levels[l], pos, adjF);
+        }
+    }
+}
+
+template <class Spec>
+__global__ void __launch_bounds__(256, 4) scatter_planes_kernel(const __grid_constant__ LaunchArgs p)
+{
+    constexpr int groups = scatter_group_count<Spec>();
+    const long long tiles = (p.numel + 255) / 256;
+    // A CTA takes 256 points through all levels, starting at a level that depends on the CTA: at any moment the CTAs of
+    // the GPU are spread over all levels, so the reductions in flight go to many different rows and L2 slices (with all
+    // CTAs on one small level, reductions to the same row queue up behind each other).
+    const int first = static_cast<int>(blockIdx.x % groups);
+    for (long long t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const long long i = t * 256 + threadIdx.x;
+        if (i >= p.numel) continue;
+        RowReader in{p.input + i * p.inS0, p.inS1};
+        for (int gi = 0; gi < groups; ++gi) {
+            int g = first + gi;
+            if (g >= groups) g -= groups;
+            scatter_group<Spec, 0>(p, g, in, i);
+        }
+    }
+}
+
+template <class Spec>
+struct PlaneLaunchers {
+    static cudaError_t scatter(const LaunchArgs& a, cudaStream_t s)
+    {
+        constexpr int groups = scatter_group_count<Spec>();
+        if constexpr (groups == 0) {
+            return cudaSuccess;
+        } else {
+            long long bx = (a.numel + 255) / 256;
+            const long long cap = static_cast<long long>(a.numSMs) * 8;
+            if (bx > cap) bx = cap;
+            if (bx < 1) bx = 1;
+            scatter_planes_kernel<Spec><<<static_cast<unsigned>(bx), 256, 0, s>>>(a);
+            return cudaGetLastError();
+        }
+    }
+};
+
 // layer-0 operand row of one point from the planes (Out writes halfs: out.half(channel, value))
 template <class Spec, int E, class Out>
 __device__ __forceinline__ void read_planes_point(const LaunchArgs& p, long long local, const Out& out)

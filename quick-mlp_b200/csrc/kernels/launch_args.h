@@ -36,6 +36,10 @@ struct GridP {
 constexpr int FLAG_GRAD_INPUT = 1;
 constexpr int FLAG_GRAD_WEIGHTS = 2;
 constexpr int FLAG_GRAD_ENCODINGS = 4;
+// the backward kernel only writes the adjoint of the grid features to level-major planes (LaunchArgs::planes); the
+// table gradients are scattered from there by KERNEL_SCATTER_PLANES. Only with FLAG_GRAD_ENCODINGS and without
+// FLAG_GRAD_INPUT.
+constexpr int FLAG_SPLIT_SCATTER = 8;
 
 struct LaunchArgs {
     long long numel;
@@ -55,7 +59,7 @@ struct LaunchArgs {
     int numGrids;
     int forcePath;                                 // 0: best path for the spec, 1: mma.sync kernels only
     int* status;                                   // device word set to 1 when a kernel gave up on a bounded wait
-    __half* planes;                                // encoded features of a chunk of points, one plane per grid level
+    __half* planes;                                // encoded features (or their adjoints) of a chunk of points, one plane per grid level
     long long planeStride;                         // points per plane (capacity of the chunk buffer)
     GridP grids[MAX_GRIDS];
 };
@@ -72,7 +76,8 @@ enum KernelId {
     KERNEL_ACTIVATION_FORWARD = 7,
     KERNEL_ACTIVATION_ADJOINT = 8,
     KERNEL_ENCODE_PLANES = 9,      // encodings of a chunk of points -> level-major feature planes
-    KERNEL_INFERENCE_PLANES = 10   // layer chain reading the feature planes instead of running the encodings
+    KERNEL_INFERENCE_PLANES = 10,  // layer chain reading the feature planes instead of running the encodings
+    KERNEL_SCATTER_PLANES = 11     // adjoint feature planes -> grid table gradients, one grid level at a time
 };
 
 // arguments of the stand-alone activation kernels

@@ -297,6 +297,54 @@ def test_autograd_binding(name):
                                      atol=1e-4 * max(1.0, float(b.abs().max())))
 
 
+@pytest.mark.parametrize("name", ["config3_small", "config4_small", "config5_small", "grid2d_add_plus_identity"])
+def test_table_gradient_scatter_paths_agree(name):
+    """Weight + table gradients without input gradients: the level-major scatter kernel (adjoint feature planes, merged
+    corner pairs) and the scatter inside the backward kernel produce the same sums."""
+    import torch
+    from qmlp import _capi, bindings
+    from qmlp._capi import check, lib, wrap
+    cfg, rng, spec, net, params, tables, acts, t_params, t_tables = _setup(name)
+    n = 20_011
+    tx = torch.from_numpy(helpers.uniform(42, 11, (n, spec.num_inputs), *rng)).cuda()
+    tadj = torch.from_numpy(helpers.uniform(42, 12, (n, spec.num_outputs), -1.0, 1.0)).cuda()
+    out = torch.empty((n, spec.num_outputs), device="cuda")
+    fwd = torch.empty((net.forward_memory(n),), dtype=torch.uint8, device="cuda")
+    assert net.adjoint_memory(n, 6) > net.adjoint_memory(n, 2) > 0
+    bwd = torch.full((net.adjoint_memory(n, 6),), 0x7e, dtype=torch.uint8, device="cuda")
+    results = []
+    try:
+        for path in (0, 1):
+            bindings.QuickMLP.set_kernel_path(path)
+            grads = torch.zeros((spec.num_parameters,), device="cuda")
+            grid_grads = [torch.zeros_like(t) if t is not None else None for t in t_tables]
+            check(lib().qmlp_network_set_parameter(net._h, wrap(t_params), _capi.QMLP_INFERENCE))
+            check(lib().qmlp_network_set_parameter(net._h, wrap(grads), _capi.QMLP_GRADIENTS))
+            for i, t in enumerate(t_tables):
+                if t is not None:
+                    net.encoding(i).set_parameter(t, _capi.QMLP_INFERENCE)
+                    net.encoding(i).set_parameter(grid_grads[i], _capi.QMLP_GRADIENTS)
+            launches = net.launch_count()
+            check(lib().qmlp_network_forward(net._h, wrap(tx), wrap(out), fwd.data_ptr(), None))
+            check(lib().qmlp_network_adjoint(net._h, wrap(tx), wrap(tadj), 6, None, fwd.data_ptr(), bwd.data_ptr(), None))
+            torch.cuda.synchronize()
+            results.append((grads, grid_grads, net.launch_count() - launches))
+    finally:
+        bindings.QuickMLP.set_kernel_path(0)
+    assert bindings.QuickMLP.device_status() == 0
+    (w0, g0, l0), (w1, g1, l1) = results
+    # the separate scatter kernel is used when every grid has two features (only then can corner pairs be merged)
+    split = all(e.n_features == 2 for e in spec.encodings if e.num_parameters)
+    assert l0 == l1 + (1 if split else 0)
+    helpers.assert_close(w0.cpu().numpy(), w1.cpu().numpy(), f"{name} weight gradient, both paths", rtol=1e-4,
+                         atol=1e-5 * max(1.0, float(w1.abs().max())))
+    for a, b in zip(g0, g1):
+        if a is not None:
+            assert float(b.abs().max()) > 0
+            helpers.assert_close(a.cpu().numpy(), b.cpu().numpy(), f"{name} table gradient, both paths", rtol=1e-3,
+                                 atol=1e-5 * max(1.0, float(b.abs().max())))
+
+
 def test_gradients_accumulate():
     """adjoint adds to the bound gradient tensors (reference: outAdjWeights[i] += ..., callers zero them)."""
     import torch
