@@ -242,6 +242,13 @@ QMLP_API int qmlp_trainer_refresh_half(qmlp_trainer_t* tr, qmlp_stream_t stream)
 QMLP_API int qmlp_trainer_gradients(qmlp_trainer_t* tr, const qmlp_tensor_t* input, const qmlp_tensor_t* target,
                                     int64_t global_points, void* workspace, size_t workspace_bytes, float* loss_sum,
                                     qmlp_stream_t stream);
+/* The same step in two parts, so that a data-parallel caller can start the all-reduce of the (large) table-gradient
+ * segments while the weight gradients are still being computed: parts = 1 runs forward, backward and the table-gradient
+ * scatter (afterwards the encoding segments of the gradient buffer are final), parts = 2 the weight/bias gradients of
+ * the layers (needs part 1 of the same batch in the same workspace), parts = 3 both. */
+QMLP_API int qmlp_trainer_gradients_part(qmlp_trainer_t* tr, const qmlp_tensor_t* input, const qmlp_tensor_t* target,
+                                         int64_t global_points, void* workspace, size_t workspace_bytes,
+                                         float* loss_sum, int parts, qmlp_stream_t stream);
 /* Adam over the fused buffer (gradient scaled by grad_scale first, e.g. 1 for a summed all-reduce of gradients
  * already normalised by global_points), refresh of the half copy, gradient buffer zeroed. step is 1-based. */
 QMLP_API int qmlp_trainer_update(qmlp_trainer_t* tr, int64_t step, float grad_scale, qmlp_stream_t stream);

@@ -870,7 +870,14 @@ int qmlp_trainer_refresh_half(qmlp_trainer_t* tr, qmlp_stream_t stream)
 int qmlp_trainer_gradients(qmlp_trainer_t* tr, const qmlp_tensor_t* input, const qmlp_tensor_t* target, int64_t global_points,
                            void* workspace, size_t workspace_bytes, float* loss_sum, qmlp_stream_t stream)
 {
+    return qmlp_trainer_gradients_part(tr, input, target, global_points, workspace, workspace_bytes, loss_sum, 3, stream);
+}
+
+int qmlp_trainer_gradients_part(qmlp_trainer_t* tr, const qmlp_tensor_t* input, const qmlp_tensor_t* target, int64_t global_points,
+                                void* workspace, size_t workspace_bytes, float* loss_sum, int parts, qmlp_stream_t stream)
+{
     QMLP_TRY
+    if (parts < 1 || parts > 3) throw std::runtime_error("parts must be 1 (up to the table gradients), 2 (weight gradients) or 3 (both)");
     if (!tr->master) throw std::runtime_error("trainer buffers are not bound");
     Network& n = *tr->net;
     std::lock_guard<std::mutex> lock(n.mutex);
@@ -899,7 +906,7 @@ int qmlp_trainer_gradients(qmlp_trainer_t* tr, const qmlp_tensor_t* input, const
     a.tS1 = target->strides[1];
     a.lossScale = static_cast<float>(2.0 / (static_cast<double>(global_points) * n.channelsOut()));
     a.lossSum = loss_sum;
-    launchNet(n, kernel::KERNEL_FORWARD_LOSS, a, stream);
+    if (parts & 1) launchNet(n, kernel::KERNEL_FORWARD_LOSS, a, stream);
     a.adjOutput = adjOut;
     a.aoS0 = n.channelsOut();
     a.aoS1 = 1;
@@ -908,8 +915,8 @@ int qmlp_trainer_gradients(qmlp_trainer_t* tr, const qmlp_tensor_t* input, const
     a.flags = kernel::FLAG_GRAD_WEIGHTS | (anyGrid ? kernel::FLAG_GRAD_ENCODINGS : 0);
     size_t pb = b + static_cast<size_t>(n32) * n.channelsOut() * 4;
     pb = (pb + 255) / 256 * 256;
-    launchBackward(n, a, anyGrid ? reinterpret_cast<__half*>(ws + pb) : nullptr, n32, stream);
-    launchNet(n, kernel::KERNEL_WGRAD, a, stream);
+    if (parts & 1) launchBackward(n, a, anyGrid ? reinterpret_cast<__half*>(ws + pb) : nullptr, n32, stream);
+    if (parts & 2) launchNet(n, kernel::KERNEL_WGRAD, a, stream);
     QMLP_CATCH
 }
 

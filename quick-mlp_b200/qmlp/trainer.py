@@ -52,14 +52,17 @@ class _CudaStep:
     def refresh_half(self):
         check(lib().qmlp_trainer_refresh_half(self._h, current_stream()))
 
-    def gradients(self, x, target, global_points, loss_sum):
+    split_gradients = True   # gradients(..., parts=1) then gradients(..., parts=2) is supported
+
+    def gradients(self, x, target, global_points, loss_sum, parts=3):
+        """parts: 1 = forward, backward, table gradients; 2 = weight/bias gradients of the layers; 3 = both."""
         b = C.c_size_t()
         check(lib().qmlp_trainer_workspace_bytes(self._h, x.shape[0], C.byref(b)))
         if self._workspace is None or self._workspace.numel() < b.value:
             self._workspace = torch.empty((b.value,), dtype=torch.uint8, device=x.device)
-        check(lib().qmlp_trainer_gradients(self._h, wrap(x), wrap(target), global_points, self._workspace.data_ptr(),
-                                           self._workspace.numel(), loss_sum.data_ptr() if loss_sum is not None else None,
-                                           current_stream()))
+        check(lib().qmlp_trainer_gradients_part(self._h, wrap(x), wrap(target), global_points, self._workspace.data_ptr(),
+                                                self._workspace.numel(), loss_sum.data_ptr() if loss_sum is not None else None,
+                                                parts, current_stream()))
 
     def update(self, step, grad_scale):
         check(lib().qmlp_trainer_update(self._h, step, grad_scale, current_stream()))
@@ -129,9 +132,20 @@ class FusedTrainer:
         dist, world = self._world()
         if global_points is None:
             global_points = world * x.shape[0]
-        self.backend.gradients(x, target, global_points, self.loss_sum)
-        if world > 1:
-            dist.all_reduce(self.gradient, op=dist.ReduceOp.SUM, group=self.process_group)
+        table_starts = [s for s in self.backend.segments[1:] if s >= 0]
+        if world > 1 and table_starts and getattr(self.backend, "split_gradients", False):
+            # The table gradients (nearly all of the vector) are final before the layers' weight gradients are computed:
+            # their all-reduce runs on the communication stream underneath the weight-gradient kernel.
+            first = min(table_starts)
+            self.backend.gradients(x, target, global_points, self.loss_sum, parts=1)
+            pending = dist.all_reduce(self.gradient[first:], op=dist.ReduceOp.SUM, group=self.process_group, async_op=True)
+            self.backend.gradients(x, target, global_points, self.loss_sum, parts=2)
+            dist.all_reduce(self.gradient[:first], op=dist.ReduceOp.SUM, group=self.process_group)
+            pending.wait()
+        else:
+            self.backend.gradients(x, target, global_points, self.loss_sum)
+            if world > 1:
+                dist.all_reduce(self.gradient, op=dist.ReduceOp.SUM, group=self.process_group)
         self.step_count += 1
         self.backend.update(self.step_count, 1.0)
 

@@ -40,17 +40,25 @@ class OracleStep:
         t = [buf[s:s + e.num_parameters].numpy() if s >= 0 else None for s, e in zip(self.segments[1:], self.spec.encodings)]
         return w, t
 
-    def gradients(self, x, target, global_points, loss_sum):
-        w, t = self._views(self.half.float())
-        out = oracle.network_forward(self.spec, w, x.numpy(), t)
-        adj = oracle.mse_loss_grad(out, target.numpy(), global_points)
-        g = oracle.network_backward(self.spec, w, x.numpy(), adj, t, want_input=False)
-        gw, gt = self._views(self.grad)
-        gw += g.grad_params
-        for a, b in zip(gt, g.grad_encodings):
-            if a is not None:
-                a += b
-        loss_sum += float(((out - target.numpy()) ** 2).sum())
+    split_gradients = True
+
+    def gradients(self, x, target, global_points, loss_sum, parts=3):
+        """parts as in qmlp_trainer_gradients_part: 1 = up to the table gradients, 2 = the layers' weight gradients."""
+        if parts & 1:
+            w, t = self._views(self.half.float())
+            out = oracle.network_forward(self.spec, w, x.numpy(), t)
+            adj = oracle.mse_loss_grad(out, target.numpy(), global_points)
+            self._pending = oracle.network_backward(self.spec, w, x.numpy(), adj, t, want_input=False)
+            _, gt = self._views(self.grad)
+            for a, b in zip(gt, self._pending.grad_encodings):
+                if a is not None:
+                    a += b
+            loss_sum += float(((out - target.numpy()) ** 2).sum())
+            self.parts_seen = getattr(self, "parts_seen", []) + [1]
+        if parts & 2:
+            gw, _ = self._views(self.grad)
+            gw += self._pending.grad_params
+            self.parts_seen = getattr(self, "parts_seen", []) + [2]
 
     def update(self, step, grad_scale):
         oracle.adam_step(self.master.numpy(), self.grad.numpy() * grad_scale, self.m.numpy(), self.v.numpy(), step)
