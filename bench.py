@@ -217,7 +217,38 @@ def run_reference_arm(args, rank, world):
                              "sample": f"{sample} points per step x {args.steps} steps"},
             "e2e": {"value": value, "unit": "points/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
+    gpu_ref = reference_gpu_kernel(key, cfg, spec, params, tables, w)
+    if gpu_ref is not None:
+        line["reference_gpu_kernel"] = gpu_ref
     print(json.dumps(line), flush=True)
+
+
+def reference_gpu_kernel(key, cfg, spec, params, tables, w):
+    """Extra figure of the reference arm: the reference's own fused inference kernel (its CUDA template filled for this
+    configuration and compiled for sm_100a by oracle/build_ref_kernels.py, its own launch configuration) timed on this
+    GPU at the workload's full batch. None when it was not built, there is no GPU, or the workload is a training step
+    (the reference has no working fused hash-grid training step to time)."""
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return None
+        import ref_kernels
+        ref = ref_kernels.ReferenceInference(cfg)
+    except Exception:
+        return None
+    n = w["points"]
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    torch.cuda.set_device(dev)
+    tp = torch.from_numpy(params.astype(np.float16)).to(dev)
+    tt = [torch.from_numpy(t).to(dev) if t is not None else None for t in tables]
+    x = torch.rand((n, spec.num_inputs), device=dev) * (w["hi"] - w["lo"]) + w["lo"]
+    ref(x, tp, tt, 3)
+    _, ms = ref(x, tp, tt, 10)
+    grid, block, smem = ref.launch_info
+    return {"value": n / (ms * 1e-3), "unit": "points/s", "ms_per_launch": ms, "points": n,
+            "kind": "reference CUDA kernel template (wmma, half accumulation, fp32 tables) compiled for sm_100a; "
+                    "inference only" + ("; forward pass of the training workload" if w["mode"] == "train" else ""),
+            "launch": {"grid": grid, "block": block, "dynamic_smem": smem}}
 
 
 # ----------------------------------------------------------------------------------------------------------------------
@@ -297,8 +328,14 @@ def main():
     else:
         net._bind(params, tables)
 
+        # tensor views and the stream handle are built once, as a C caller would hold them: at 2^16 points the kernel
+        # takes a few microseconds and per-call Python work would be what is timed
+        views = [(wrap(x), wrap(o)) for x, o in zip(xs, outs)]
+        stream_handle = current_stream()
+
         def step(i):
-            check(lib().qmlp_network_inference(net._h, wrap(xs[i % nsets]), wrap(outs[i % nsets]), current_stream()))
+            vx, vo = views[i % nsets]
+            check(lib().qmlp_network_inference(net._h, vx, vo, stream_handle))
 
     def barrier():
         if world > 1:
@@ -313,19 +350,41 @@ def main():
     if rank == 0:
         sampler.start()
         time.sleep(0.15)
+    # A launch-bound workload (a few microseconds of kernel per step) is captured, K steps in a row, in one CUDA graph
+    # and the timed region is one replay of it: otherwise the host's launch rate is what gets measured.
+    graph = None
+    if trainer is None and n <= (1 << 17):
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            handle = current_stream()
+            for i in range(args.steps):
+                vx, vo = views[i % nsets]
+                check(lib().qmlp_network_inference(net._h, vx, vo, handle))
+        graph.replay()
+        torch.cuda.synchronize()
     events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     barrier()
     t0 = time.perf_counter()
-    for i in range(args.steps):
-        events[i][0].record(stream)
-        step(i)
-        events[i][1].record(stream)
+    if graph is not None:
+        events[0][0].record(stream)
+        graph.replay()
+        events[-1][1].record(stream)
+    else:
+        for i in range(args.steps):
+            events[i][0].record(stream)
+            step(i)
+            events[i][1].record(stream)
     barrier()
     wall = time.perf_counter() - t0
     clocks = sampler.stop() if rank == 0 else None
     launches = net.launch_count() - launches0
-    dev_ms = [a.elapsed_time(b) for a, b in events]
     span_ms = events[0][0].elapsed_time(events[-1][1])        # whole timed region on the device
+    if graph is not None:
+        launches = args.steps                                   # counted at capture; the replay launches the same K kernels
+        dev_ms = [span_ms / args.steps] * args.steps
+    else:
+        dev_ms = [a.elapsed_time(b) for a, b in events]
     t = torch.tensor([span_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -396,6 +455,11 @@ def main():
                         "steps": e2e_steps},
                 "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
                 "wall_s_timed_region": wall}
+        if graph is not None:
+            line["config"]["launch"] = "the K steps are one CUDA graph (launch-bound workload); the timed region is one replay"
+        if w["mode"] == "train":
+            line["config"]["parallelism"] = (f"dp{world}: all-reduce of the table gradients under the weight-gradient kernel, "
+                                             "then of the network gradients")
         if not args.no_cpu_baseline and world == 1:
             try:
                 line["cpu_baseline"] = cpu_baseline(key)

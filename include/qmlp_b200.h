@@ -80,10 +80,12 @@ QMLP_API const char* qmlp_get_kernel_cache_dir(void);
 /* Directory holding the kernel template headers used to instantiate a spec. */
 QMLP_API int qmlp_set_kernel_include_dir(const char* dir);
 
-/* Kernel family used for fused inference: 0 = the best one instantiated for the spec (tcgen05 tensor-core kernel when
- * the layer widths allow it; a level-major encoding pass in front of it when the grid tables are much larger than L2,
+/* Kernel family used for fused inference: 0 = the best one instantiated for the spec and the batch (tcgen05 tensor-core
+ * kernel when the layer widths allow it and the batch fills its tile slots, else the mma.sync kernel; a level-major
+ * encoding pass in front of the tcgen05 kernel when the grid tables are much larger than L2,
  * which makes the network keep a feature buffer of up to 2^22 points and 512 MB from its first such call until it is
- * destroyed), 1 = the mma.sync kernels only, 2 = the level-major pass for every grid network. Takes the place of the
+ * destroyed), 1 = the mma.sync kernels only, 2 = the level-major pass for every grid network, 3 = the tcgen05 kernel at
+ * any batch size. Takes the place of the
  * reference's per-kernel tuning options (overwrite_blocksize_*, skew_shared_memory;
  * src_cpp/src/fused_network.cpp:45-69). */
 QMLP_API int qmlp_set_kernel_path(int path);

@@ -209,7 +209,8 @@ int qmlp_set_kernel_include_dir(const char* dir) { Library::instance().includeDi
 int qmlp_set_kernel_path(int path)
 {
     QMLP_TRY
-    if (path < 0 || path > 2) throw std::runtime_error("kernel path must be 0 (best for the spec), 1 (mma.sync only) or 2 (level-major grid pass)");
+    if (path < 0 || path > 3)
+        throw std::runtime_error("kernel path must be 0 (best for spec and batch), 1 (mma.sync only), 2 (level-major grid pass) or 3 (tcgen05 at any batch size)");
     Library::instance().kernelPath = path;
     QMLP_CATCH
 }

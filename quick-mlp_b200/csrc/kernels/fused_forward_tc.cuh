@@ -182,6 +182,8 @@ struct TcLayout {
     __host__ __device__ static constexpr int slotsPerWarpgroup() { return warpgroups() < 8 && fits(2 * warpgroups()) ? 2 : 1; }
     __host__ __device__ static constexpr int loadWidth() { return warpgroups() == 8 ? 32 : 64; }
     __host__ __device__ static constexpr int slots() { return warpgroups() * slotsPerWarpgroup(); }
+    // points one CTA has in flight when every slot holds a tile
+    __host__ __device__ static constexpr long long pointsPerCta() { return static_cast<long long>(TC_TILE) * slots(); }
     // tensor-memory allocation: a power of two >= 32 columns
     __host__ __device__ static constexpr int tmemCols()
     {

@@ -790,7 +790,12 @@ struct NetworkLaunchers {
         switch (kernel) {
         case KERNEL_INFERENCE:
             if constexpr (TcLayout<Spec>::eligible()) {
-                if (a.forcePath != 1) { e = TcLaunchers<Spec>::inference(a, s); break; }
+                // The tcgen05 kernel pays a fixed price per launch (tensor-memory allocation, operand staging for 148
+                // large CTAs) and needs at least one 128-point tile per slot to use what it sets up; below that the
+                // mma.sync kernel is quicker (config 1 at 2^16 points: 2.7 us against 4.7 us; config 2 at 2^16: 11.5
+                // against 12.9 us, at 2^20: 89 against 62 us).
+                const bool enough = a.numel >= TcLayout<Spec>::pointsPerCta() * a.numSMs;
+                if (a.forcePath == 3 || (a.forcePath != 1 && enough)) { e = TcLaunchers<Spec>::inference(a, s); break; }
             }
             e = forward<0>(a, s);
             break;

@@ -57,7 +57,7 @@ struct LaunchArgs {
     int flags;
     int numSMs;
     int numGrids;
-    int forcePath;                                 // 0: best path for the spec, 1: mma.sync kernels only
+    int forcePath;                                 // 0: best path for spec and batch, 1: mma.sync kernels only, 3: tcgen05 whenever instantiated
     int* status;                                   // device word set to 1 when a kernel gave up on a bounded wait
     __half* planes;                                // encoded features (or their adjoints) of a chunk of points, one plane per grid level
     long long planeStride;                         // points per plane (capacity of the chunk buffer)

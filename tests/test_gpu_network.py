@@ -79,11 +79,20 @@ def test_spec_layout_matches_oracle(name):
 
 @pytest.mark.parametrize("name", list(network_cases().keys()))
 @pytest.mark.parametrize("n", [1, 33, 1000])
-def test_inference(name, n):
+@pytest.mark.parametrize("path", [0, 3])
+def test_inference(name, n, path):
+    """path 0: the kernel the library picks for this batch (the mma.sync kernel at these sizes); path 3: the tcgen05
+    kernel regardless of the batch size (falls back to mma.sync for specs wider than 128)."""
     import torch
+    from qmlp import bindings
     cfg, rng, spec, net, params, tables, acts, t_params, t_tables = _setup(name)
     x = helpers.uniform(42, 1, (n, spec.num_inputs), *rng)
-    out = net.inference(torch.from_numpy(x).cuda(), t_params, t_tables).cpu().numpy()
+    try:
+        bindings.QuickMLP.set_kernel_path(path)
+        out = net.inference(torch.from_numpy(x).cuda(), t_params, t_tables).cpu().numpy()
+    finally:
+        bindings.QuickMLP.set_kernel_path(0)
+    assert bindings.QuickMLP.device_status() == 0
     emu = oracle.network_forward(spec, params, x, tables, half=True, activations=acts)
     ref = oracle.network_forward(spec, params, x, tables, half=False, activations=acts)
     assert np.isfinite(out).all()
@@ -92,7 +101,7 @@ def test_inference(name, n):
 
 
 @pytest.mark.parametrize("name", ["config2", "uneven", "custom_act", "config4_small", "config5_small"])
-@pytest.mark.parametrize("n", [127, 128, 5000, 40001])
+@pytest.mark.parametrize("n", [127, 128, 5000, 40001, 200_000])
 def test_tensor_core_paths_agree(name, n):
     """The tcgen05 inference kernel and the mma.sync kernel compute the same function (same rounding points: fp32
     accumulate, one rounding to half per layer), and no kernel reports a timed-out on-chip wait."""
@@ -101,7 +110,7 @@ def test_tensor_core_paths_agree(name, n):
     cfg, rng, spec, net, params, tables, acts, t_params, t_tables = _setup(name)
     x = torch.from_numpy(helpers.uniform(42, 7, (n, spec.num_inputs), *rng)).cuda()
     try:
-        bindings.QuickMLP.set_kernel_path(0)
+        bindings.QuickMLP.set_kernel_path(3)
         out_best = net.inference(x, t_params, t_tables)
         bindings.QuickMLP.set_kernel_path(1)
         out_mma = net.inference(x, t_params, t_tables)

@@ -1,0 +1,153 @@
+"""Parity with the reference's OWN device code: its fused inference kernel template
+(src_cpp/include/qmlp/kernels/network_forward.cuh with layer.cuh, encoding_identity.cuh, encoding_hashgrid.cuh), filled
+per configuration the way FusedNetwork::compileInferenceKernel fills it and compiled for sm_100a by
+oracle/build_ref_kernels.py, runs beside this build's kernels on the same inputs and parameters.
+
+The reference kernel accumulates in half (kernels/layer.cuh:110) where this build accumulates in fp32, so the two are
+compared with north_star's tolerance |a-b| <= 1e-2 |b| + 1e-3 and both are compared with the fp32 oracle."""
+import json
+import os
+import sys
+
+import numpy as np
+import pytest
+
+import helpers
+import qmlp_oracle as oracle
+import specs
+
+pytestmark = pytest.mark.gpu
+
+
+def _reference(cfg):
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle"))
+    import ref_kernels
+    try:
+        return ref_kernels.ReferenceInference(cfg)
+    except FileNotFoundError:
+        pytest.skip("reference kernels were not built (no reference checkout at build time)")
+
+
+CASES = {
+    "config1": (specs.config1, (0.0, 1.0), 65536),
+    "config2": (specs.config2, (-1.0, 1.0), 100_003),
+    "config3_small": (lambda: specs.config3(log2_hashmap_size=14), (0.0, 1.0), 50_001),
+    "config5_small": (lambda: specs.config5(log2_hashmap_size=12), (0.0, 1.0), 20_000),
+}
+
+
+@pytest.mark.parametrize("name", list(CASES))
+@pytest.mark.parametrize("path", [1, 3])
+def test_inference_matches_reference_kernel(name, path):
+    """path 1: this build's mma.sync kernel, path 3: its tcgen05 kernel."""
+    import torch
+    from qmlp import bindings
+    make, rng, n = CASES[name]
+    cfg = make()
+    ref = _reference(cfg)
+    spec = oracle.parse_spec(cfg)
+    params = helpers.xavier_parameters(spec, cfg, bias_scale=0.05).astype(np.float16)
+    tables = helpers.grid_tables(spec, scale=0.5)
+    x = helpers.uniform(42, 21, (n, spec.num_inputs), *rng)
+    tx = torch.from_numpy(x).cuda()
+    tp = torch.from_numpy(params).cuda()
+    tt = [torch.from_numpy(t).cuda() if t is not None else None for t in tables]
+
+    out_ref, _ = ref(tx, tp, tt)
+    net = bindings.Network(json.dumps(cfg))
+    try:
+        bindings.QuickMLP.set_kernel_path(path)
+        out = net.inference(tx, tp, tt)
+    finally:
+        bindings.QuickMLP.set_kernel_path(0)
+    torch.cuda.synchronize()
+    assert bindings.QuickMLP.device_status() == 0
+    a, b = out.cpu().numpy(), out_ref.cpu().numpy()
+    assert np.isfinite(b).all()
+    helpers.assert_close(a, b, f"{name}: this build vs the reference kernel", rtol=1e-2, atol=1e-3, max_violations=0.01)
+    # both against the independent fp32 oracle, the reference's own 5 % allowance for half-precision arithmetic
+    o32 = oracle.network_forward(spec, params.astype(np.float32), x, tables, half=False)
+    helpers.assert_close(b, o32, f"{name}: reference kernel vs fp32 oracle", rtol=1e-2, atol=2e-3, max_violations=0.05)
+    helpers.assert_close(a, o32, f"{name}: this build vs fp32 oracle", rtol=1e-2, atol=2e-3, max_violations=0.05)
+    # this build is at least as close to fp32 as the reference's half-accumulating kernel
+    assert np.abs(a - o32).mean() <= np.abs(b - o32).mean() * 1.05 + 1e-6
+
+
+def _reference_backward(cfg):
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle"))
+    import ref_kernels
+    try:
+        return ref_kernels.ReferenceBackward(cfg)
+    except FileNotFoundError:
+        pytest.skip("reference kernels were not built (no reference checkout at build time)")
+
+
+@pytest.mark.parametrize("name", ["config1", "config2", "config3_small"])
+def test_backward_matches_reference_kernel(name):
+    """The reference's NetworkKernelBackward, fed with the forward stash of THIS build (both use (N32, Cout) row-major
+    pre-activations per layer, src_cpp/src/fused_network.cpp:207-218), against this build's backward kernel: the delta
+    of every layer (what the weight gradients are computed from), the input gradient of identity encodings and the
+    table gradient of the hash grid. Sharing the stash keeps activation derivatives identical on both sides; what
+    remains is half (reference) against fp32 (here) accumulation in the delta chain."""
+    import ctypes as C
+    import torch
+    from qmlp import _capi, bindings
+    from qmlp._capi import check, lib, wrap
+    make, rng, _ = CASES[name]
+    cfg = make()
+    ref = _reference_backward(cfg)
+    spec = oracle.parse_spec(cfg)
+    n = 10_007
+    n32 = (n + 31) // 32 * 32
+    params = helpers.xavier_parameters(spec, cfg, bias_scale=0.05).astype(np.float16)
+    tables = helpers.grid_tables(spec, scale=0.5)
+    tx = torch.from_numpy(helpers.uniform(42, 31, (n, spec.num_inputs), *rng)).cuda()
+    tadj = torch.from_numpy(helpers.uniform(42, 32, (n, spec.num_outputs), -1.0, 1.0)).cuda()
+    tp = torch.from_numpy(params).cuda()
+    tt = [torch.from_numpy(t).cuda() if t is not None else None for t in tables]
+
+    net = bindings.Network(json.dumps(cfg))
+    out = torch.empty((n, spec.num_outputs), device="cuda")
+    fwd = torch.zeros((net.forward_memory(n) // 2,), dtype=torch.float16, device="cuda")
+    bwd = torch.zeros((net.adjoint_memory(n) // 2,), dtype=torch.float16, device="cuda")
+    grads = torch.zeros((spec.num_parameters,), device="cuda")
+    adj_in = torch.zeros_like(tx)
+    grid_grads = [torch.zeros_like(t) if t is not None else None for t in tt]
+    check(lib().qmlp_network_set_parameter(net._h, wrap(tp), _capi.QMLP_INFERENCE))
+    check(lib().qmlp_network_set_parameter(net._h, wrap(grads), _capi.QMLP_GRADIENTS))
+    for i, t in enumerate(tt):
+        if t is not None:
+            net.encoding(i).set_parameter(t, _capi.QMLP_INFERENCE)
+            net.encoding(i).set_parameter(grid_grads[i], _capi.QMLP_GRADIENTS)
+    check(lib().qmlp_network_forward(net._h, wrap(tx), wrap(out), fwd.data_ptr(), None))
+    ai = wrap(adj_in)
+    check(lib().qmlp_network_adjoint(net._h, wrap(tx), wrap(tadj), 7, C.byref(ai), fwd.data_ptr(), bwd.data_ptr(), None))
+    torch.cuda.synchronize()
+    assert bindings.QuickMLP.device_status() == 0
+
+    cin0 = spec.layers[0].channels_in
+    stash_halfs = sum(l.channels_out for l in spec.layers)
+    pre = fwd[n32 * cin0: n32 * (cin0 + stash_halfs)]
+    ref_grid_grads = [torch.zeros_like(t) if t is not None else None for t in tt]
+    ref_adj_in, ref_deltas = ref(tx, tadj, tp, pre, tt, ref_grid_grads)
+
+    off = 0
+    for li, l in enumerate(spec.layers):
+        c = l.channels_out
+        mine = bwd[n32 * off: n32 * (off + c)].view(n32, c)[:n].float().cpu().numpy()
+        theirs = ref_deltas[n32 * off: n32 * (off + c)].view(n32, c)[:n].float().cpu().numpy()
+        if li == len(spec.layers) - 1:      # padded output channels carry no adjoint
+            mine, theirs = mine[:, :spec.num_outputs], theirs[:, :spec.num_outputs]
+        scale = max(1e-3, float(np.abs(theirs).max()))
+        helpers.assert_close(mine, theirs, f"{name}: delta of layer {li}", rtol=1e-2, atol=2e-3 * scale, max_violations=0.01)
+        off += c
+    has_grid = any(e.num_parameters for e in spec.encodings)
+    if not has_grid:
+        a, b = adj_in.cpu().numpy(), ref_adj_in.cpu().numpy()
+        helpers.assert_close(a, b, f"{name}: input gradient", rtol=1e-2, atol=2e-3 * max(1e-3, float(np.abs(b).max())),
+                             max_violations=0.01)
+    for g, r in zip(grid_grads, ref_grid_grads):
+        if g is not None:
+            a, b = g.cpu().numpy(), r.cpu().numpy()
+            assert float(np.abs(b).max()) > 0
+            helpers.assert_close(a, b, f"{name}: table gradient", rtol=1e-2, atol=2e-3 * float(np.abs(b).max()), max_violations=0.01)
