@@ -85,6 +85,8 @@ class CpuNetwork:
         layers = (_Layer * len(spec.layers))()
         for i, l in enumerate(spec.layers):
             layers[i].channels_in, layers[i].channels_out = l.channels_in, l.channels_out
+            if not isinstance(l.activation, str):
+                raise ValueError("the C++ CPU restatement handles one activation per layer (benchmark configurations)")
             layers[i].use_bias, layers[i].activation = int(l.use_bias), _ACT[l.activation]
             layers[i].weights_start, layers[i].bias_start = l.weights_start, l.bias_start
         self._encs, self._layers = encs, layers

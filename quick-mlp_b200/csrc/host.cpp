@@ -410,14 +410,17 @@ Network::Network(const Json& cfg, const std::string& parent)
                 if (static_cast<int>(ae.size()) != s.channelsOut)
                     throw configuration_error(format("If you specify individual activations per channel, then the number of activations (%d) must match the number of output channels (%d)",
                                                      static_cast<int>(ae.size()), s.channelsOut));
-                // as in the reference (fused_network.cpp:447): parsed, but only a uniform array can be instantiated
+                // the reference parses such arrays and then refuses them at code generation (fused_network.cpp:447);
+                // here a non-uniform array becomes a per-channel functor (generateSource)
+                bool uniform = true;
                 for (const auto& e2 : ae.items()) {
                     if (!e2.isString()) throw configuration_error("Per-channel activations must be specified as a string");
                     Activation_ptr a = activationFactory.get(e2.asString());
-                    if (s.activation && s.activation->id() != a->id())
-                        throw std::runtime_error("Individual activations per channel are not implemented yet");
-                    s.activation = a;
+                    if (!s.perChannel.empty() && s.perChannel.front()->id() != a->id()) uniform = false;
+                    s.perChannel.push_back(a);
                 }
+                s.activation = s.perChannel.front();
+                if (uniform) s.perChannel.clear();
             } else {
                 throw configuration_error("Unknown type for the activations, expected string or array");
             }
@@ -613,12 +616,35 @@ std::string Network::generateSource(unsigned halfMask) const
 {
     std::ostringstream s;
     s << "// fused-network instantiation; layers:";
-    for (const auto& l : layers_) s << " " << l.channelsIn << "->" << l.channelsOut << (l.useBias ? "+b" : "") << ":" << l.activation->id();
+    for (const auto& l : layers_)
+        s << " " << l.channelsIn << "->" << l.channelsOut << (l.useBias ? "+b" : "") << ":"
+          << (l.perChannel.empty() ? l.activation->id() : std::string("per-channel"));
     s << "\n#include \"standalone.cuh\"\nusing namespace qmlp::kernel;\nnamespace {\nnamespace activations {\n";
     std::set<std::string> seen;
-    for (const auto& l : layers_)
+    for (const auto& l : layers_) {
         if (!l.activation->isBuiltin() && seen.insert(l.activation->id()).second) s << l.activation->functorDefinition();
+        for (const auto& a : l.perChannel)
+            if (!a->isBuiltin() && seen.insert(a->id()).second) s << a->functorDefinition();
+    }
     s << "}\n";
+    // per-channel arrays: one functor per such layer, an if-chain over runs of equal activations; the padding
+    // channels behind the last one pass values through (they carry zeros)
+    for (int i = 0; i < numLayers(); ++i) {
+        const auto& pc = layers_[i].perChannel;
+        if (pc.empty()) continue;
+        std::ostringstream fwd, adj;
+        size_t b = 0;
+        while (b < pc.size()) {
+            size_t e = b;
+            while (e < pc.size() && pc[e]->id() == pc[b]->id()) ++e;
+            fwd << "        if (c < " << e << ") return " << pc[b]->functorName() << "::forward(x);\n";
+            adj << "        if (c < " << e << ") return " << pc[b]->functorName() << "::adjoint(x, adjz);\n";
+            b = e;
+        }
+        s << "struct PerChannelAct" << i << " : PerChannelActivation<PerChannelAct" << i << "> {\n"
+          << "    static __device__ __forceinline__ half forward1(half x, int c)\n    {\n" << fwd.str() << "        return x;\n    }\n"
+          << "    static __device__ __forceinline__ half adjoint1(half x, half adjz, int c)\n    {\n" << adj.str() << "        return adjz;\n    }\n};\n";
+    }
     int maxWidth = 0;
     for (const auto& l : layers_) maxWidth = std::max(maxWidth, std::max(l.channelsIn, l.channelsOut));
     const int nl = numLayers();
@@ -636,7 +662,9 @@ std::string Network::generateSource(unsigned halfMask) const
     arr("WOFF", [](const LayerSpec& l) { return static_cast<long long>(l.weightsStart); });
     arr("BOFF", [](const LayerSpec& l) { return static_cast<long long>(l.biasStart); });
     s << "    template <int L> struct Act;\n    template <int E> struct Enc;\n};\n";
-    for (int i = 0; i < nl; ++i) s << "template <> struct Spec::Act<" << i << "> : " << layers_[i].activation->functorName() << " {};\n";
+    for (int i = 0; i < nl; ++i)
+        s << "template <> struct Spec::Act<" << i << "> : "
+          << (layers_[i].perChannel.empty() ? layers_[i].activation->functorName() : "PerChannelAct" + std::to_string(i)) << " {};\n";
     int off = 0, slot = 0;
     for (int i = 0; i < numEncodings(); ++i) {
         const auto& e = encodings_[i];

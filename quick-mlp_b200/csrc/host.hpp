@@ -177,7 +177,8 @@ Encoding_ptr createEncoding(const Json& cfg); // EncodingFactory::create, src_cp
 struct LayerSpec {
     int channelsIn = 0, channelsOut = 0;
     bool useBias = false;
-    Activation_ptr activation;
+    Activation_ptr activation;                   // the layer's activation, or the first entry of a per-channel array
+    std::vector<Activation_ptr> perChannel;      // one per (unpadded) output channel when the array is not uniform
     int64_t weightsStart = 0, biasStart = -1;
 };
 

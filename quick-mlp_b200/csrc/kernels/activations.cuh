@@ -8,6 +8,7 @@
 #pragma once
 #include <cuda_fp16.h>
 #include <stdint.h>
+#include <type_traits>
 
 // helpers user snippets may reference (src_cpp/include/qmlp/kernels/common.cuh:16-19)
 __device__ __forceinline__ half hZERO() { return __ushort_as_half(0); }
@@ -111,6 +112,62 @@ struct BuiltinIdentity {
     static __device__ __forceinline__ half forward(half x) { return x; }
     static __device__ __forceinline__ half adjoint(half, half adjz) { return adjz; }
     static __device__ __forceinline__ __half2 forward_f32x2(float a, float b) { return __floats2half2_rn(a, b); }
+};
+
+// ---- per-channel activation arrays -----------------------------------------------------------------------------------
+// A layer may name one activation per output channel ("activation": [...], src_cpp/src/fused_network.cpp:106-125; the
+// reference parses such arrays and then refuses to generate code for them, :447). The generated functor of such a layer
+// declares PER_CHANNEL and takes the channel of the first of the two values; the kernels call through these helpers,
+// which drop the channel for ordinary functors.
+template <class A, class = void>
+struct is_per_channel : std::false_type {};
+template <class A>
+struct is_per_channel<A, std::void_t<decltype(A::PER_CHANNEL)>> : std::true_type {};
+
+template <class A>
+__device__ __forceinline__ __half2 act_forward2(__half2 x, int channel)
+{
+    if constexpr (is_per_channel<A>::value) return A::forward2c(x, channel);
+    else return A::forward2(x);
+}
+template <class A>
+__device__ __forceinline__ __half2 act_adjoint2(__half2 x, __half2 adjz, int channel)
+{
+    if constexpr (is_per_channel<A>::value) return A::adjoint2c(x, adjz, channel);
+    else return A::adjoint2(x, adjz);
+}
+template <class A>
+__device__ __forceinline__ __half2 act_forward_f32x2(float a, float b, int channel)
+{
+    if constexpr (is_per_channel<A>::value) return A::forward2c(__floats2half2_rn(a, b), channel);
+    else return A::forward_f32x2(a, b);
+}
+
+// both values belong to the same channel (fragments that pair two points of one channel)
+template <class A>
+__device__ __forceinline__ __half2 act_forward2_same_channel(__half2 x, int channel)
+{
+    if constexpr (is_per_channel<A>::value) return A::forward2s(x, channel);
+    else return A::forward2(x);
+}
+
+// Base of a generated per-channel functor: D supplies forward1(half, channel) and adjoint1(half, half, channel).
+template <class D>
+struct PerChannelActivation {
+    static constexpr bool PER_CHANNEL = true;
+    static __device__ __forceinline__ __half2 forward2c(__half2 x, int c)
+    {
+        return __halves2half2(D::forward1(__low2half(x), c), D::forward1(__high2half(x), c + 1));
+    }
+    static __device__ __forceinline__ __half2 forward2s(__half2 x, int c)
+    {
+        return __halves2half2(D::forward1(__low2half(x), c), D::forward1(__high2half(x), c));
+    }
+    static __device__ __forceinline__ __half2 adjoint2c(__half2 x, __half2 adjz, int c)
+    {
+        return __halves2half2(D::adjoint1(__low2half(x), __low2half(adjz), c),
+                              D::adjoint1(__high2half(x), __high2half(adjz), c + 1));
+    }
 };
 
 } // namespace kernel

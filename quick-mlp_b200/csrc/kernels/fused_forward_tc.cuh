@@ -344,7 +344,8 @@ __device__ __forceinline__ bool tc_stage(const LaunchArgs& p, TcSlot& sl, uint64
                     if (c0 + g * 16 >= NCOL) continue;
                     uint32_t packed[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) packed[i] = h2_as_u32(Act::forward_f32x2(v[g * 16 + 2 * i], v[g * 16 + 2 * i + 1]));
+                    for (int i = 0; i < 8; ++i)
+                        packed[i] = h2_as_u32(act_forward_f32x2<Act>(v[g * 16 + 2 * i], v[g * 16 + 2 * i + 1], c0 + g * 16 + 2 * i));
                     const int chunk = (c0 + g * 16) / 8;
                     if constexpr (!LAST) {
                         // row of the next layer's A operand: two 16-byte chunks
@@ -484,12 +485,11 @@ struct TcLaunchers {
         using TL = TcLayout<Spec>;
         constexpr int smem = TL::totalBytes();
         constexpr int threads = TL::warpgroups() * 128;
-        static bool configured = false;
+        static DeviceOnce once;   // function attributes are per device
         auto k = fused_forward_tc_kernel<Spec, PLANES>;
-        if (!configured) {
+        if (once.first()) {
             cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
             if (e != cudaSuccess) return e;
-            configured = true;
         }
         const long long tiles = (a.numel + TC_TILE - 1) / TC_TILE;
         long long blocks = tiles < a.numSMs ? tiles : a.numSMs;

@@ -16,6 +16,8 @@
 //   template<int L> struct Act  : activation functor of layer L
 //   template<int E> struct Enc  : EncIdentity<...> or EncGrid<...>
 #pragma once
+#include <atomic>
+
 #include "launch_args.h"
 #include "mma.cuh"
 #include "activations.cuh"
@@ -223,7 +225,7 @@ __device__ __forceinline__ void forward_layers(const LaunchArgs& p, const __half
                     if (row0 < p.numel) *reinterpret_cast<__half2*>(st + row0 * COUT + col) = lo;
                     if (row0 + 8 < p.numel) *reinterpret_cast<__half2*>(st + (row0 + 8) * COUT + col) = hi;
                 }
-                const __half2 zlo = Act::forward2(lo), zhi = Act::forward2(hi);
+                const __half2 zlo = act_forward2<Act>(lo, col), zhi = act_forward2<Act>(hi, col);
                 if constexpr (!LAST) {
                     aOut[m][j][h * 2 + 0] = h2_as_u32(zlo);
                     aOut[m][j][h * 2 + 1] = h2_as_u32(zhi);
@@ -420,7 +422,7 @@ __device__ __forceinline__ void backward_layers(const LaunchArgs& p, const __hal
                 const int col = k * 16 + (e >> 1) * 8 + q * 2;
                 __half2 x = __float2half2_rn(0.f);
                 if (row < p.numel) x = *reinterpret_cast<const __half2*>(pre + row * COUT + col);
-                const __half2 d = Act::adjoint2(x, u32_as_h2(adj[m][k][e]));
+                const __half2 d = act_adjoint2<Act>(x, u32_as_h2(adj[m][k][e]), col);
                 adj[m][k][e] = h2_as_u32(d);
                 if constexpr ((FLAGS & FLAG_GRAD_WEIGHTS) != 0) {
                     if (row < p.numel) *reinterpret_cast<__half2*>(dl + row * COUT + col) = d;
@@ -624,7 +626,8 @@ __device__ __forceinline__ void wgrad_layer(const LaunchArgs& p, unsigned char* 
                 if constexpr (L > 0) {
                     using ActPrev = typename Spec::template Act<(L > 0 ? L - 1 : 0)>;
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) bf[e] = h2_as_u32(ActPrev::forward2(u32_as_h2(bf[e])));
+                    for (int e = 0; e < 4; ++e)   // a register pairs two points of channel nb*16 + (e>>1)*8 + lane/4
+                        bf[e] = h2_as_u32(act_forward2_same_channel<ActPrev>(u32_as_h2(bf[e]), nb * 16 + (e >> 1) * 8 + (lane >> 2)));
                 }
                 mma16816(acc[b][0], af, bf[0], bf[1]);
                 mma16816(acc[b][1], af, bf[2], bf[3]);
@@ -685,6 +688,18 @@ wgrad_kernel(const __grid_constant__ LaunchArgs p)
 
 // ---- host-side launchers (compiled into each instantiation) -------------------------------------------------------
 template <class Spec> struct TcLayout;     // fused_forward_tc.cuh
+// "first call on the current device" latch for per-device kernel attributes (a process may drive several GPUs)
+struct DeviceOnce {
+    std::atomic<unsigned long long> seen{0};
+    bool first()
+    {
+        int d = 0;
+        cudaGetDevice(&d);
+        const unsigned long long bit = 1ull << (d & 63);
+        return (seen.fetch_or(bit) & bit) == 0;
+    }
+};
+
 template <class Spec> struct TcLaunchers;
 template <class Spec> struct PlaneLaunchers;
 
@@ -700,12 +715,11 @@ struct NetworkLaunchers {
     static cudaError_t forward(const LaunchArgs& a, cudaStream_t s)
     {
         constexpr int smem = SmemLayout<Spec>::totalBytes();
-        static bool configured = false;
+        static DeviceOnce once;   // function attributes are per device
         auto k = fused_forward_kernel<Spec, MODE>;
-        if (!configured) {
+        if (once.first()) {
             cudaError_t e = setSmem(k, smem);
             if (e != cudaSuccess) return e;
-            configured = true;
         }
         int perSM = 0;
         cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSM, k, Spec::WARPS * 32, smem);
@@ -724,12 +738,11 @@ struct NetworkLaunchers {
     static cudaError_t backwardT(const LaunchArgs& a, cudaStream_t s)
     {
         constexpr int smem = SmemLayout<Spec>::totalBytes();
-        static bool configured = false;
+        static DeviceOnce once;   // function attributes are per device
         auto k = fused_backward_kernel<Spec, FLAGS>;
-        if (!configured) {
+        if (once.first()) {
             cudaError_t e = setSmem(k, smem);
             if (e != cudaSuccess) return e;
-            configured = true;
         }
         int perSM = 0;
         cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSM, k, Spec::WARPS * 32, smem);
@@ -766,12 +779,11 @@ struct NetworkLaunchers {
     static cudaError_t wgrad(const LaunchArgs& a, cudaStream_t s)
     {
         constexpr int smem = WgradSmem<Spec>::bytes();
-        static bool configured = false;
+        static DeviceOnce once;   // function attributes are per device
         auto k = wgrad_kernel<Spec>;
-        if (!configured) {
+        if (once.first()) {
             cudaError_t e = setSmem(k, smem);
             if (e != cudaSuccess) return e;
-            configured = true;
         }
         const long long slabs = (a.numel + WG_SLAB - 1) / WG_SLAB;
         long long gx = (static_cast<long long>(a.numSMs) * 2 + Spec::NUM_LAYERS - 1) / Spec::NUM_LAYERS;

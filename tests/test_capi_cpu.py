@@ -92,6 +92,10 @@ def test_configuration_errors():
     bad(lambda c: c["network"][0].update(activation=["relu"] * 3))             # per-channel list of the wrong length
     bad(lambda c: c["encodings"][0].update(n_in=7), QmlpError)                 # grid dimension outside [1, 6]
     bad(lambda c: c.update(activation_specification=["no/such/file.json"]))
+    # a per-channel list of the right length is accepted, mixed activations included (the reference stops at code generation)
+    mixed = specs.config3(12)
+    mixed["network"][0].update(activation=["relu"] * 40 + ["sine"] * 24)
+    assert bindings.Network(json.dumps(mixed)).num_layers() == 3
     with pytest.raises(QmlpError):
         bindings.Network("{ not json")
     with pytest.raises(QmlpError):

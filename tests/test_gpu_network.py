@@ -34,6 +34,12 @@ def network_cases():
         "ref_widths": (specs.identity_net(16, [32, 48, 16], ["celu", "identity", "celu"], bias=False), (-1.0, 1.0), "reference"),
         "uneven": (specs.identity_net(5, [20, 23, 7], ["sine", "relu", "identity"], bias=[True, False, True]), (-1.0, 1.0), "reference"),
         "custom_act": (specs.identity_net(4, [32, 32, 2], ["leaky", "sine", "leaky"], bias=True, extra_activations=[LEAKY]), (-1.0, 1.0), "reference"),
+        # one activation per output channel (the reference parses such arrays and refuses them at code generation,
+        # src_cpp/src/fused_network.cpp:106-125, 447): runs of built-ins, a user snippet, and a uniform array
+        "per_channel": (specs.identity_net(4, [24, 20, 16, 3],
+                                           [["relu"] * 8 + ["sine"] * 10 + ["celu"] * 6, ["identity"] * 5 + ["leaky"] * 15,
+                                            ["celu"] * 16, "identity"], bias=True, extra_activations=[LEAKY]),
+                        (-1.0, 1.0), "reference"),
         "config3_small": (specs.config3(log2_hashmap_size=12), (0.0, 1.0), "xavier"),
         "config4_small": (specs.config4(log2_hashmap_size=10, dense_resolution=16), (0.0, 1.0), "xavier"),
         "config5_small": (specs.config5(log2_hashmap_size=12), (0.0, 1.0), "xavier"),
@@ -100,7 +106,7 @@ def test_inference(name, n, path):
     helpers.assert_close(out, ref, f"{name} inference vs fp32 oracle", max_violations=helpers.MAX_VIOLATIONS)
 
 
-@pytest.mark.parametrize("name", ["config2", "uneven", "custom_act", "config4_small", "config5_small"])
+@pytest.mark.parametrize("name", ["config2", "uneven", "custom_act", "per_channel", "config4_small", "config5_small"])
 @pytest.mark.parametrize("n", [127, 128, 5000, 40001, 200_000])
 def test_tensor_core_paths_agree(name, n):
     """The tcgen05 inference kernel and the mma.sync kernel compute the same function (same rounding points: fp32
