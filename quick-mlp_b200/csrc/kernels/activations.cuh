@@ -83,6 +83,8 @@ struct BuiltinCelu {
         asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 1.4426950408889634f));
         return x > 0.f ? x : e - 1.f;
     }
+    // (a half2 form from the rounding on - pack, ex2.approx.f16x2, subtract, select - has fewer instructions but measured
+    // 5 % slower in the tcgen05 epilogue and less accurate than the fp32 form)
     static __device__ __forceinline__ __half2 forward_f32x2(float a, float b) { return __floats2half2_rn(celu_f32(a), celu_f32(b)); }
 };
 

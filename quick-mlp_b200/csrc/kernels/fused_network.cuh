@@ -540,7 +540,7 @@ fused_backward_kernel(const __grid_constant__ LaunchArgs p)
 // dW_l (COUT x CIN) += sum_n delta_l[n,:]^T * a_{l-1}[n,:],  db_l += sum_n delta_l[n,:]
 // (math of tests_cpp/test_against_eigen2.cpp:187-200; replaces the single-block WeightUpdateSingleBlockKernel,
 // src_cpp/include/qmlp/kernels/network_weight_update_block.cuh:356-494). a_{l-1} is recomputed from the stashed
-// pre-activation (or is the stashed encoded input for l == 0). blockIdx.y selects the layer, blockIdx.x strides
+// pre-activation (or is the stashed encoded input for l == 0). Each CTA works on one layer (WgradSplit) and strides
 // over 64-point slabs; partial sums are added to the fp32 gradient vector with red.global.add.
 constexpr int WG_SLAB = 64;
 constexpr int WG_WARPS = 8;
@@ -552,8 +552,44 @@ struct WgradSmem {
     __host__ __device__ static constexpr int bytes() { return 2 * WG_SLAB * ((maxCout() + 8) + (maxCin() + 8)) * 2; }
 };
 
+// CTAs of the one-dimensional grid are dealt to the layers in proportion to the bytes a layer reads per point
+// (delta row + input row): the kernel is bound by that traffic, and an equal share per layer leaves the narrow layers'
+// CTAs idle while the wide ones finish (config 4: 176 : 192 : 80 : 32).
+template <class Spec>
+struct WgradSplit {
+    __host__ __device__ static constexpr int weight(int l) { return Spec::CIN[l] + Spec::COUT[l]; }
+    __host__ __device__ static constexpr int total()
+    {
+        int t = 0;
+        for (int i = 0; i < Spec::NUM_LAYERS; ++i) t += weight(i);
+        return t;
+    }
+    // smallest grid that gives every layer at least one CTA
+    __host__ __device__ static constexpr int minCtas()
+    {
+        int m = weight(0);
+        for (int i = 1; i < Spec::NUM_LAYERS; ++i) m = weight(i) < m ? weight(i) : m;
+        return (total() + m - 1) / m;
+    }
+    __host__ __device__ static constexpr long long prefix(int l)
+    {
+        long long s = 0;
+        for (int i = 0; i < l; ++i) s += weight(i);
+        return s;
+    }
+    // first CTA of layer L in a grid of `ctas` (layer L owns [begin<L>, begin<L + 1>))
+    template <int L>
+    __host__ __device__ static int begin(int ctas)
+    {
+        constexpr long long before = prefix(L);
+        constexpr long long all = total();
+        return static_cast<int>(before * ctas / all);
+    }
+};
+
+// `cta` of `ctas`: this CTA's rank among the CTAs working on layer L
 template <class Spec, int L>
-__device__ __forceinline__ void wgrad_layer(const LaunchArgs& p, unsigned char* smem)
+__device__ __forceinline__ void wgrad_layer(const LaunchArgs& p, unsigned char* smem, int cta, int ctas)
 {
     using SL = SmemLayout<Spec>;
     constexpr int CIN = Spec::CIN[L], COUT = Spec::COUT[L];
@@ -598,12 +634,12 @@ __device__ __forceinline__ void wgrad_layer(const LaunchArgs& p, unsigned char* 
         }
     };
 
-    long long slab = blockIdx.x;
+    long long slab = cta;
     int buf = 0;
     if (slab < numSlabs) load_slab(slab, 0);
     cp_async_commit();
-    for (; slab < numSlabs; slab += gridDim.x) {
-        const long long next = slab + gridDim.x;
+    for (; slab < numSlabs; slab += ctas) {
+        const long long next = slab + ctas;
         if (next < numSlabs) load_slab(next, buf ^ 1);
         cp_async_commit();
         cp_async_wait<1>();
@@ -673,7 +709,8 @@ template <class Spec, int L>
 __device__ __forceinline__ void wgrad_dispatch(const LaunchArgs& p, unsigned char* smem)
 {
     if constexpr (L < Spec::NUM_LAYERS) {
-        if (blockIdx.y == L) wgrad_layer<Spec, L>(p, smem);
+        const int first = WgradSplit<Spec>::template begin<L>(gridDim.x), end = WgradSplit<Spec>::template begin<L + 1>(gridDim.x);
+        if (static_cast<int>(blockIdx.x) < end) wgrad_layer<Spec, L>(p, smem, blockIdx.x - first, end - first);
         else wgrad_dispatch<Spec, L + 1>(p, smem);
     }
 }
@@ -785,12 +822,12 @@ struct NetworkLaunchers {
             cudaError_t e = setSmem(k, smem);
             if (e != cudaSuccess) return e;
         }
+        // two CTAs per SM, fewer for small batches, never fewer than every layer needs to get one
         const long long slabs = (a.numel + WG_SLAB - 1) / WG_SLAB;
-        long long gx = (static_cast<long long>(a.numSMs) * 2 + Spec::NUM_LAYERS - 1) / Spec::NUM_LAYERS;
-        if (gx > slabs) gx = slabs;
-        if (gx < 1) gx = 1;
-        dim3 grid(static_cast<unsigned>(gx), Spec::NUM_LAYERS);
-        k<<<grid, WG_WARPS * 32, smem, s>>>(a);
+        long long ctas = static_cast<long long>(a.numSMs) * 2;
+        if (ctas > slabs * Spec::NUM_LAYERS) ctas = slabs * Spec::NUM_LAYERS;
+        if (ctas < WgradSplit<Spec>::minCtas()) ctas = WgradSplit<Spec>::minCtas();
+        k<<<static_cast<unsigned>(ctas), WG_WARPS * 32, smem, s>>>(a);
         return cudaGetLastError();
     }
 
