@@ -1,6 +1,7 @@
 """qmlp.FusedActivation, API of src_py/qmlp/activation.py:8-79."""
 import torch
 
+from . import ops  # noqa: F401  (registers torch.ops.qmlp_b200.*)
 from .bindings import Activation
 
 
@@ -31,7 +32,8 @@ class FusedActivation(torch.nn.Module):
         self._activation = Activation(cfg)
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:
-        return self._activation.forward(input)
+        # a registered operator keyed by the configuration string: traceable, freezable, saveable (qmlp/ops.py)
+        return torch.ops.qmlp_b200.activation_forward(input, self._cfg)
 
     def __repr__(self):
         return f"FusedActivation(\"{self._cfg}\")"

@@ -1,6 +1,7 @@
 """qmlp.FusedEncoding, API of src_py/qmlp/encoding.py:9-122."""
 import torch
 
+from . import ops  # noqa: F401  (registers torch.ops.qmlp_b200.*)
 from .bindings import Encoding
 
 
@@ -36,9 +37,8 @@ class FusedEncoding(torch.nn.Module):
         return t
 
     def forward(self, input: torch.Tensor, parameters: torch.Tensor = None) -> torch.Tensor:
-        if parameters is None:
-            return self._encoding.forward(input)
-        return self._encoding.forward_with_parameter(input, parameters)
+        # a registered operator keyed by the configuration string: traceable, freezable, saveable (qmlp/ops.py)
+        return torch.ops.qmlp_b200.encoding_forward(input, parameters, self._cfg)
 
     def __repr__(self):
         return f'FusedEncoding("""{self._cfg}""")'
