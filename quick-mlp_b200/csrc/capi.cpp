@@ -120,7 +120,7 @@ void launchBackward(Network& n, kernel::LaunchArgs& a, __half* planes, int64_t n
     bool gridGrad = false;
     for (int i = 0; i < a.numGrids; ++i) gridGrad = gridGrad || a.grids[i].grad != nullptr;
     for (int i = 0; i < n.numEncodings(); ++i)
-        if (auto* g = dynamic_cast<EncodingHashGrid*>(n.encoding(i).get())) gridGrad = gridGrad && g->features() == 2;
+        if (auto* g = dynamic_cast<EncodingHashGrid*>(n.encoding(i).get())) gridGrad = gridGrad && g->features() == 2 && !g->isLine();
     const bool split = planes != nullptr && gridGrad && (a.flags & kernel::FLAG_GRAD_ENCODINGS) != 0 &&
                        (a.flags & kernel::FLAG_GRAD_INPUT) == 0 && Library::instance().kernelPath != 1;
     if (split) {

@@ -278,10 +278,12 @@ EncodingHashGrid::EncodingHashGrid(const Json& cfg)
         throw std::runtime_error("grid too large: element offsets are 32-bit as in the reference kernels");
 }
 
-Json EncodingHashGrid::toJson() const
+Json EncodingHashGrid::toJson() const { return gridJson(); }
+
+Json EncodingHashGrid::gridJson() const
 {
     Json j = Json::object();
-    j.set("id", Json::string(id()));
+    j.set("id", Json::string("HashGrid"));
     j.set("start_in", Json::number(start_));
     j.set("n_in", Json::number(dim_));
     j.set("n_levels", Json::number(levels_));
@@ -332,7 +334,9 @@ void EncodingHashGrid::fillGrid(kernel::GridP& g) const
     for (int i = 0; i < kernel::MAX_GRID_DIMS; ++i) {
         g.boxMin[i] = i < dim_ ? boxMin_[i] : 0.f;
         g.boxInvSize[i] = i < dim_ ? boxInvSize_[i] : 1.f;
+        g.boxSize[i] = i < dim_ ? boxSize_[i] : 1.f;
     }
+    g.stepsize = 0.f;
     for (int l = 0; l < levels_; ++l) {
         g.levels[l].offset = static_cast<unsigned int>(table_[l].memoryOffset);
         g.levels[l].resolution = table_[l].resolution;
@@ -351,11 +355,60 @@ void EncodingHashGrid::fillGrid(kernel::GridP& g) const
     g.vecOk = ok ? 1 : 0;
 }
 
+// child volume of a line integration: a hash grid that reads the sample position, channels 0 .. n_in-1
+// (parseChild, src_cpp/src/encoding_line_integration.cpp:31-39)
+static Json lineChildConfig(const Json& cfg)
+{
+    Json child = cfg.at("volume");
+    if (!child.isObject() || child.at("id").asString() != "HashGrid")
+        throw configuration_error("Child encoding for LineIntegration could not be created");
+    child.set("start_in", Json::number(0));
+    child.set("n_in", Json::number(cfg.at("n_in").asInt()));
+    return child;
+}
+
+EncodingLineIntegration::EncodingLineIntegration(const Json& cfg)
+    : EncodingHashGrid(lineChildConfig(cfg)), rayStart_(cfg.at("start_in").asInt()),
+      stepsize_(static_cast<float>(cfg.at("stepsize").asDouble())), average_(cfg.at("blending").asString() == "average")
+{
+    // unknown blending strings map to the first enum entry, additive (NLOHMANN_JSON_SERIALIZE_ENUM,
+    // src_cpp/src/encoding_line_integration.cpp:9-12)
+    if (!(stepsize_ > 0.f)) throw std::runtime_error(format("Stepsize must be positive, but is %g", stepsize_));
+    if (rayStart_ < 0) throw configuration_error(format("Start channel must be non-negative, but is %d", rayStart_));
+    // the reference's ray / box intersection is written for three dimensions only (encoding_line_integration.cuh:13-49)
+    if (dim_ != 3) throw configuration_error(format("LineIntegration needs a three-dimensional volume, but n_in is %d", dim_));
+}
+
+Json EncodingLineIntegration::toJson() const
+{
+    Json j = Json::object();
+    j.set("id", Json::string(id()));
+    j.set("start_in", Json::number(rayStart_));
+    j.set("n_in", Json::number(dim_));
+    j.set("volume", gridJson());
+    j.set("stepsize", Json::number(stepsize_));
+    j.set("blending", Json::string(average_ ? "average" : "additive"));
+    return j;
+}
+
+std::string EncodingLineIntegration::deviceType(int outOffset, int slot, bool halfTable) const
+{
+    return format("EncLine<%d, %d, %d, %d, %s, %d, %d, %s, %s>", rayStart_, dim_, levels_, features_, concat_ ? "true" : "false",
+                  outOffset, slot, halfTable ? "true" : "false", average_ ? "true" : "false");
+}
+
+void EncodingLineIntegration::fillGrid(kernel::GridP& g) const
+{
+    EncodingHashGrid::fillGrid(g);
+    g.stepsize = stepsize_;
+}
+
 Encoding_ptr createEncoding(const Json& cfg)
 {
     const std::string id = cfg.at("id").asString();
     if (id == "Identity") return std::make_shared<EncodingIdentity>(cfg);
     if (id == "HashGrid") return std::make_shared<EncodingHashGrid>(cfg);
+    if (id == "LineIntegration") return std::make_shared<EncodingLineIntegration>(cfg);
     throw configuration_error(format("No encoding with id '%s' found", id.c_str()));
 }
 
@@ -648,6 +701,8 @@ std::string Network::generateSource(unsigned halfMask) const
     int maxWidth = 0;
     for (const auto& l : layers_) maxWidth = std::max(maxWidth, std::max(l.channelsIn, l.channelsOut));
     const int nl = numLayers();
+    bool anyLine = false;
+    for (const auto& e : encodings_) anyLine = anyLine || e->isLine();
     auto arr = [&](const char* name, auto get) {
         s << "    static constexpr int " << name << "[" << nl << "] = {";
         for (int i = 0; i < nl; ++i) s << (i ? ", " : "") << get(layers_[i]);
@@ -656,7 +711,8 @@ std::string Network::generateSource(unsigned halfMask) const
     s << "struct Spec {\n"
       << "    static constexpr int NUM_INPUTS = " << channelsIn_ << ", NUM_OUTPUTS = " << channelsOut_ << ", NUM_LAYERS = " << nl
       << ", ENC_CHANNELS = " << encodedChannels_ << ", NUM_ENCODINGS = " << numEncodings() << ";\n"
-      << "    static constexpr int WARPS = 8, MIN_BLOCKS = " << (maxWidth <= 64 ? 2 : 1) << ";\n";
+      << "    static constexpr int WARPS = 8, MIN_BLOCKS = " << (maxWidth <= 64 ? 2 : 1) << ";\n"
+      << "    static constexpr bool HAS_LINE = " << (anyLine ? "true" : "false") << ";\n";
     arr("CIN", [](const LayerSpec& l) { return static_cast<long long>(l.channelsIn); });
     arr("COUT", [](const LayerSpec& l) { return static_cast<long long>(l.channelsOut); });
     arr("WOFF", [](const LayerSpec& l) { return static_cast<long long>(l.weightsStart); });

@@ -110,7 +110,8 @@ public:
     virtual int numOutputChannels() const = 0;
     virtual bool hasParameters() const { return false; }
     virtual int64_t parameterCount() const { return 0; }
-    virtual bool isGrid() const { return false; }
+    virtual bool isGrid() const { return false; }   // owns a grid table (a slot of LaunchArgs::grids)
+    virtual bool isLine() const { return false; }   // line integration over its grid
     // C++ type of the device-side descriptor, e.g. "EncGrid<0,3,16,2,true,0,0,false>"
     virtual std::string deviceType(int outOffset, int slot, bool halfTable) const = 0;
     virtual void setParameter(const qmlp_tensor_t* t, int usage);
@@ -160,8 +161,9 @@ public:
     void fillGrid(kernel::GridP& g) const override;
     const std::vector<GridLevel>& levelTable() const { return table_; }
     int features() const { return features_; }
+    Json gridJson() const;   // the hash grid's own configuration (id "HashGrid")
 
-private:
+protected:
     int start_, dim_, levels_, features_, log2Hashmap_, hashmapSize_, minRes_, maxRes_;
     bool concat_;
     bool hasScale_ = false;
@@ -169,6 +171,25 @@ private:
     std::vector<float> boxMin_, boxSize_, boxInvSize_;
     std::vector<GridLevel> table_;
     int64_t numParameters_ = 0;
+};
+
+// EncodingLineIntegration, src_cpp/include/qmlp/encoding_line_integration.h / src_cpp/src/encoding_line_integration.cpp:
+// ray start + direction in, the child volume (a hash grid on the sample position) integrated along the ray out.
+// The child's table is this encoding's parameter.
+class EncodingLineIntegration : public EncodingHashGrid {
+public:
+    explicit EncodingLineIntegration(const Json& cfg);
+    Json toJson() const override;
+    std::string id() const override { return "LineIntegration"; }
+    int maxInputChannel() const override { return rayStart_ + dim_ * 2 - 1; }
+    bool isLine() const override { return true; }
+    std::string deviceType(int outOffset, int slot, bool halfTable) const override;
+    void fillGrid(kernel::GridP& g) const override;
+
+private:
+    int rayStart_;
+    float stepsize_;
+    bool average_;
 };
 
 Encoding_ptr createEncoding(const Json& cfg); // EncodingFactory::create, src_cpp/src/iencoding.cpp:221-228

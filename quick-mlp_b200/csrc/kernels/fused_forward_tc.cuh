@@ -193,7 +193,8 @@ struct TcLayout {
     }
     __host__ __device__ static constexpr bool eligible()
     {
-        return maxCout() <= 128 && maxCin() <= 128 && fits(1);
+        // (the plane kernels that come with this path know identity and grid encodings only)
+        return maxCout() <= 128 && maxCin() <= 128 && fits(1) && !Spec::HAS_LINE;
     }
     __host__ __device__ static constexpr int aStart() { return weightBytes(); }
     __host__ __device__ static constexpr int biasStart() { return aStart() + slots() * aBytes(); }

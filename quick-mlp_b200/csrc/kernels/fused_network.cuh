@@ -32,15 +32,27 @@ constexpr int MT = 2;
 // ---- encoding descriptors ------------------------------------------------------------------------------------
 template <int START_, int N_, int OUT_OFF_>
 struct EncIdentity {
-    static constexpr bool IS_GRID = false;
+    static constexpr bool IS_GRID = false, IS_LINE = false;
     static constexpr int START = START_, N = N_, OUT_OFF = OUT_OFF_, NUM_OUT = N_;
 };
 template <int START_, int D_, int L_, int F_, bool CONCAT_, int OUT_OFF_, int SLOT_, bool HALF_TABLE_>
 struct EncGrid {
-    static constexpr bool IS_GRID = true;
+    static constexpr bool IS_GRID = true, IS_LINE = false;
     static constexpr int START = START_, D = D_, L = L_, F = F_, OUT_OFF = OUT_OFF_, SLOT = SLOT_;
     static constexpr bool CONCAT = CONCAT_, HALF_TABLE = HALF_TABLE_;
     static constexpr int NUM_OUT = CONCAT_ ? L_ * F_ : F_;
+};
+
+// Line integration over a grid (src_cpp/include/qmlp/kernels/encoding_line_integration.cuh:51-166): the input holds a
+// ray start and a ray direction (2 * D channels from START); the grid is sampled every GridP::stepsize along the part of
+// the ray inside the grid's bounding box and the samples are summed (AVERAGE: divided by the number of steps).
+template <int START_, int D_, int L_, int F_, bool CONCAT_, int OUT_OFF_, int SLOT_, bool HALF_TABLE_, bool AVERAGE_>
+struct EncLine {
+    static constexpr bool IS_GRID = false, IS_LINE = true;
+    static constexpr int START = START_, D = D_, L = L_, F = F_, OUT_OFF = OUT_OFF_, SLOT = SLOT_;
+    static constexpr bool CONCAT = CONCAT_, HALF_TABLE = HALF_TABLE_, AVERAGE = AVERAGE_;
+    static constexpr int NUM_OUT = CONCAT_ ? L_ * F_ : F_;
+    static_assert(D_ == 3, "the ray / bounding-box intersection exists for three dimensions only");
 };
 
 // ---- shared memory layout ------------------------------------------------------------------------------------
@@ -121,12 +133,115 @@ struct HalfRowReader {
     __device__ __forceinline__ float operator()(int c) const { return __half2float(row[c]); }
 };
 
+// ---- line integration ------------------------------------------------------------------------------------------------
+// ray start / direction from the input and the parameter interval inside the bounding box
+// (IntersectionRayAABB<3>, encoding_line_integration.cuh:27-49: slab test, same operation order)
+template <class Enc, class In>
+__device__ __forceinline__ void line_ray(const GridP& g, const In& in, float (&start)[3], float (&dir)[3], float& tmin, float& tmax)
+{
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+        start[i] = in(i + Enc::START);
+        dir[i] = in(i + Enc::START + 3);
+    }
+    const float inv0 = 1.0f / dir[0], inv1 = 1.0f / dir[1], inv2 = 1.0f / dir[2];
+    const float t1 = (g.boxMin[0] - start[0]) * inv0, t2 = (g.boxMin[0] + g.boxSize[0] - start[0]) * inv0;
+    const float t3 = (g.boxMin[1] - start[1]) * inv1, t4 = (g.boxMin[1] + g.boxSize[1] - start[1]) * inv1;
+    const float t5 = (g.boxMin[2] - start[2]) * inv2, t6 = (g.boxMin[2] + g.boxSize[2] - start[2]) * inv2;
+    tmin = fmaxf(fmaxf(fminf(t1, t2), fminf(t3, t4)), fminf(t5, t6));
+    tmax = fminf(fminf(fmaxf(t1, t2), fmaxf(t3, t4)), fmaxf(t5, t6));
+}
+
+// unit-cube position of the sample at parameter t (fma(t, dir, start), then the grid's own box transform)
+template <class Enc>
+__device__ __forceinline__ void line_sample(const GridP& g, const float (&start)[3], const float (&dir)[3], float t, float (&pos)[3])
+{
+#pragma unroll
+    for (int i = 0; i < 3; ++i) pos[i] = (fmaf(t, dir[i], start[i]) - g.boxMin[i]) * g.boxInvSize[i];
+}
+
+template <class Enc, class In, class Out>
+__device__ __forceinline__ void line_forward(const GridP& g, const In& in, const Out& out)
+{
+    float start[3], dir[3], tmin, tmax;
+    line_ray<Enc>(g, in, start, dir, tmin, tmax);
+    float acc[Enc::NUM_OUT];
+#pragma unroll
+    for (int i = 0; i < Enc::NUM_OUT; ++i) acc[i] = 0.f;
+    for (float t = tmin; t < tmax; t += g.stepsize) {   // encoding_line_integration.cuh:79-85
+        float pos[3];
+        line_sample<Enc>(g, start, dir, t, pos);
+        for (int l = 0; l < Enc::L; ++l) {
+            float feat[Enc::F];
+            grid_level_forward<3, Enc::F, Enc::HALF_TABLE>(g, g.levels[l], pos, feat);
+#pragma unroll
+            for (int i = 0; i < Enc::F; ++i) acc[(Enc::CONCAT ? l * Enc::F : 0) + i] += feat[i];
+        }
+    }
+    if constexpr (Enc::AVERAGE) {
+        const int steps = static_cast<int>(floorf((tmax - tmin) / g.stepsize));
+        if (steps > 0) {
+            const float s = 1.0f / static_cast<float>(steps);
+#pragma unroll
+            for (int i = 0; i < Enc::NUM_OUT; ++i) acc[i] *= s;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < Enc::NUM_OUT; ++i) out(Enc::OUT_OFF + i, acc[i]);
+}
+
+// encoding_line_integration.cuh:101-165; the position gradient of a sample goes to the ray start and, times t, to the
+// ray direction (the dependence of tmin / tmax on the ray is ignored, as in the reference)
+template <class Enc, bool INPUT_GRAD, bool PARAM_GRAD, class In, class AdjOut>
+__device__ __forceinline__ void line_adjoint(const GridP& g, const In& in, const AdjOut& adjOut, float* adjInRow, long long aiS1)
+{
+    const bool paramGrad = PARAM_GRAD && g.grad != nullptr;
+    float start[3], dir[3], tmin, tmax;
+    line_ray<Enc>(g, in, start, dir, tmin, tmax);
+    float scale = 1.0f;
+    if constexpr (Enc::AVERAGE) {
+        const int steps = static_cast<int>(floorf((tmax - tmin) / g.stepsize));
+        scale = steps > 0 ? 1.0f / static_cast<float>(steps) : 1.0f;
+    }
+    float adjStart[3] = {0.f, 0.f, 0.f}, adjDir[3] = {0.f, 0.f, 0.f};
+    for (float t = tmin; t < tmax; t += g.stepsize) {
+        float pos[3], adjPos[3] = {0.f, 0.f, 0.f};
+        line_sample<Enc>(g, start, dir, t, pos);
+        for (int l = 0; l < Enc::L; ++l) {
+            float adjF[Enc::F];
+#pragma unroll
+            for (int i = 0; i < Enc::F; ++i) adjF[i] = scale * adjOut(Enc::OUT_OFF + (Enc::CONCAT ? l * Enc::F : 0) + i);
+            if (paramGrad)
+                grid_level_adjoint<3, Enc::F, Enc::HALF_TABLE, true, INPUT_GRAD>(g, g.levels[l], pos, adjF, adjPos);
+            else if constexpr (INPUT_GRAD)
+                grid_level_adjoint<3, Enc::F, Enc::HALF_TABLE, false, true>(g, g.levels[l], pos, adjF, adjPos);
+        }
+        if constexpr (INPUT_GRAD) {
+#pragma unroll
+            for (int k = 0; k < 3; ++k) {
+                const float a = adjPos[k] * g.boxInvSize[k];
+                adjStart[k] += a;
+                adjDir[k] += a * t;
+            }
+        }
+    }
+    if constexpr (INPUT_GRAD) {
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+            adjInRow[(k + Enc::START) * aiS1] += adjStart[k];
+            adjInRow[(k + Enc::START + 3) * aiS1] += adjDir[k];
+        }
+    }
+}
+
 template <class Spec, int E, class Out>
 __device__ __forceinline__ void encode_point(const LaunchArgs& p, const RowReader& in, const Out& out)
 {
     if constexpr (E < Spec::NUM_ENCODINGS) {
         using Enc = typename Spec::template Enc<E>;
-        if constexpr (!Enc::IS_GRID) {
+        if constexpr (Enc::IS_LINE) {
+            line_forward<Enc>(p.grids[Enc::SLOT], in, out);
+        } else if constexpr (!Enc::IS_GRID) {
             // src_cpp/include/qmlp/kernels/encoding_identity.cuh:16-25
 #pragma unroll
             for (int i = 0; i < Enc::N; ++i) out(Enc::OUT_OFF + i, in(i + Enc::START));
@@ -324,7 +439,9 @@ __device__ __forceinline__ void encode_adjoint_point(const LaunchArgs& p, const 
 {
     if constexpr (E < Spec::NUM_ENCODINGS) {
         using Enc = typename Spec::template Enc<E>;
-        if constexpr (!Enc::IS_GRID) {
+        if constexpr (Enc::IS_LINE) {
+            line_adjoint<Enc, INPUT_GRAD, PARAM_GRAD>(p.grids[Enc::SLOT], in, adjOut, adjInRow, aiS1);
+        } else if constexpr (!Enc::IS_GRID) {
             // src_cpp/include/qmlp/kernels/encoding_identity.cuh:27-38
             if constexpr (INPUT_GRAD) {
 #pragma unroll

@@ -26,6 +26,8 @@ struct GridP {
     float* grad;       // fp32 gradient table, same layout (may be null)
     float boxMin[MAX_GRID_DIMS];
     float boxInvSize[MAX_GRID_DIMS];
+    float boxSize[MAX_GRID_DIMS];
+    float stepsize;    // line integration only: world-space step along the ray
     int tableIsHalf;
     int vecOk; // table and grad pointers are aligned for whole-row vector access
     GridLevelP levels[MAX_GRID_LEVELS];

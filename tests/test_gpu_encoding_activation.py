@@ -25,6 +25,12 @@ def encoding_cases():
         "hash3d_f3_add": specs.hashgrid(3, 4, 3, 9, 8, 128, combination_mode="add", start_in=2, box_min=[-2, -2, -2], box_size=[4, 4, 4]),
         "hash2d_f8": specs.hashgrid(2, 4, 8, 8, 8, 256),
         "dense6d": specs.hashgrid(6, 2, 1, -1, 2, 3),
+        # ray start + direction in, the grid integrated along the ray out (src_cpp/src/encoding_line_integration.cpp)
+        "line_average": {"id": "LineIntegration", "start_in": 1, "n_in": 3, "stepsize": 0.05, "blending": "average",
+                         "volume": specs.hashgrid(3, 4, 2, 10, 4, 32)},
+        "line_additive_add": {"id": "LineIntegration", "start_in": 0, "n_in": 3, "stepsize": 0.11, "blending": "additive",
+                              "volume": specs.hashgrid(3, 3, 4, 9, 4, 24, combination_mode="add", box_min=[-1, -1, -1],
+                                                       box_size=[2, 2, 2])},
     }
 
 
@@ -36,7 +42,36 @@ def _enc(name):
     return cfg, e, oe
 
 
-@pytest.mark.parametrize("name", list(encoding_cases().keys()))
+@pytest.mark.parametrize("name", ["line_average", "line_additive_add"])
+def test_line_integration(name):
+    """Rays that start in and around the volume's bounding box, with arbitrary directions (some miss the box): output,
+    table gradient and ray gradients against the oracle's restatement of encoding_line_integration.cuh:61-165."""
+    import torch
+    cfg, e, oe = _enc(name)
+    n = 301
+    bmin, bsize = float(cfg["volume"]["bounding_box_min"][0]), float(cfg["volume"]["bounding_box_size"][0])
+    x = helpers.uniform(7, 1, (n, oe.start_in + 7), bmin - 0.4 * bsize, bmin + 1.4 * bsize)
+    x[:, oe.start_in + 3:oe.start_in + 6] = helpers.uniform(7, 2, (n, 3), -1.0, 1.0)
+    adj = helpers.uniform(7, 3, (n, oe.num_outputs), -1, 1)
+    assert e.num_output_channels() == oe.num_outputs and e.max_input_channel() == oe.start_in + 5
+    assert e.parameter_count() == oe.num_parameters and json.loads(e.to_json())["id"] == "LineIntegration"
+    table = helpers.uniform(7, 4, (oe.num_parameters,), -1, 1)
+    tx = torch.from_numpy(x).cuda().requires_grad_(True)
+    tp = torch.from_numpy(table).cuda().requires_grad_(True)
+    out = e.forward_with_parameter(tx, tp)
+    expect = oracle.grid_forward(oe, x, table)
+    assert float(np.abs(expect).sum(axis=1).min()) == 0.0 and float(np.abs(expect).max()) > 0.1   # misses and hits
+    scale = float(np.abs(expect).max())
+    helpers.assert_close(out.detach().cpu().numpy(), expect, f"{name} forward", rtol=1e-3, atol=1e-4 * scale, max_violations=0.01)
+    out.backward(torch.from_numpy(adj).cuda())
+    g, ai = oracle.grid_adjoint(oe, x, table, adj, True, True)
+    helpers.assert_close(tp.grad.cpu().numpy(), g, f"{name} table gradient", rtol=1e-3, atol=1e-4 * float(np.abs(g).max()),
+                         max_violations=0.01)
+    helpers.assert_close(tx.grad.cpu().numpy(), ai, f"{name} ray gradient", rtol=2e-3, atol=1e-3 * float(np.abs(ai).max()),
+                         max_violations=0.01)
+
+
+@pytest.mark.parametrize("name", [k for k in encoding_cases() if not k.startswith("line_")])
 def test_encoding_forward_and_adjoint(name):
     import torch
     cfg, e, oe = _enc(name)

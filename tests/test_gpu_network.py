@@ -40,6 +40,12 @@ def network_cases():
                                            [["relu"] * 8 + ["sine"] * 10 + ["celu"] * 6, ["identity"] * 5 + ["leaky"] * 15,
                                             ["celu"] * 16, "identity"], bias=True, extra_activations=[LEAKY]),
                         (-1.0, 1.0), "reference"),
+        # rays (start, direction) integrated through a hash grid, plus the raw ray as identity features
+        "line_net": ({"num_inputs": 6, "num_outputs": 3, "activation_specification": specs.BUILTIN,
+                      "encodings": [{"id": "LineIntegration", "start_in": 0, "n_in": 3, "stepsize": 0.07, "blending": "average",
+                                     "volume": specs.hashgrid(3, 4, 4, 10, 4, 32)},
+                                    {"id": "Identity", "start_in": 0, "n_in": 6}],
+                      "network": specs.mlp([32, 3], ["celu", "identity"], True)}, (-0.3, 1.3), "xavier"),
         "config3_small": (specs.config3(log2_hashmap_size=12), (0.0, 1.0), "xavier"),
         "config4_small": (specs.config4(log2_hashmap_size=10, dense_resolution=16), (0.0, 1.0), "xavier"),
         "config5_small": (specs.config5(log2_hashmap_size=12), (0.0, 1.0), "xavier"),
