@@ -96,6 +96,19 @@ struct SmemLayout {
     }
 };
 
+// CTAs per SM the forward and backward kernels are compiled for: two (a 128-register budget per thread, which costs
+// the 128-wide networks a few dozen bytes of spills but doubles the warps that hide gather and stash latency) whenever
+// two copies of the shared-memory plan fit on an SM, else one.
+template <class Spec>
+__host__ __device__ constexpr int resident_ctas()
+{
+#ifdef QMLP_RESIDENT_CTAS
+    return QMLP_RESIDENT_CTAS;
+#else
+    return 2 * (SmemLayout<Spec>::totalBytes() + 1024) <= 227 * 1024 ? 2 : 1;
+#endif
+}
+
 template <class Spec, int L>
 __device__ __forceinline__ void stage_layer(const LaunchArgs& p, __half* sW, __half* sB)
 {
@@ -370,7 +383,7 @@ __device__ __forceinline__ void forward_layers(const LaunchArgs& p, const __half
 }
 
 template <class Spec, int MODE>
-__global__ void __launch_bounds__(Spec::WARPS * 32, Spec::MIN_BLOCKS)
+__global__ void __launch_bounds__(Spec::WARPS * 32, resident_ctas<Spec>())
 fused_forward_kernel(const __grid_constant__ LaunchArgs p)
 {
     using SL = SmemLayout<Spec>;
@@ -611,7 +624,7 @@ __device__ __forceinline__ void backward_layers(const LaunchArgs& p, const __hal
 }
 
 template <class Spec, int FLAGS>
-__global__ void __launch_bounds__(Spec::WARPS * 32, Spec::MIN_BLOCKS)
+__global__ void __launch_bounds__(Spec::WARPS * 32, resident_ctas<Spec>())
 fused_backward_kernel(const __grid_constant__ LaunchArgs p)
 {
     using SL = SmemLayout<Spec>;

@@ -134,7 +134,8 @@ def make_activations():
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    # the reference checkout: first argument, else a directory "reference" beside this repository
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.path.normpath(os.path.join(HERE, os.pardir, os.pardir, os.pardir, "reference"))
     make_mlp(ref)
     make_grid()
     make_activations()
