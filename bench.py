@@ -402,9 +402,9 @@ def main():
         hloss = torch.empty((1,), dtype=torch.float32).pin_memory()
 
         def e2e_step(i):
-            xd = xs[i % nsets]; td = targets[i % nsets]
-            xd.copy_(hx, non_blocking=True); td.copy_(ht, non_blocking=True)
-            trainer.step(xd, td)
+            # the public host-memory step: this step's batch was uploaded while the previous step ran (prefetch of the
+            # following batch on a copy stream); the loss comes back to the host every step
+            trainer.step_host(hx, ht, next_batch=(hx, ht))
             hloss.copy_(trainer.loss_sum, non_blocking=True)
             torch.cuda.current_stream().synchronize()
         h2d, d2h = hx.numel() * 4 + ht.numel() * 4, 4

@@ -337,6 +337,7 @@ static void inferenceLocked(Network& n, const qmlp_tensor_t* input, qmlp_tensor_
         int64_t cap = 1 << 16;
         while (cap < (1 << 22) && cap * 2 * rowBytes <= (512ll << 20)) cap *= 2;
         const int64_t need = std::min<int64_t>(cap, (a.numel + 65535) / 65536 * 65536);
+        n.claimDevice();
         if (n.planeCapacity < need) {
             if (n.planes) {
                 checkCuda(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)), "cudaStreamSynchronize");
@@ -402,6 +403,7 @@ int qmlp_network_inference_host(qmlp_network_t* net, const float* host_input, fl
         while (chunk < (1 << 20) && chunk * 8 < num_points) chunk *= 2;
     }
     chunk = std::min(chunk, num_points);
+    n.claimDevice();
     HostPipeline& hp = n.hostPipeline;
     hp.reserve(chunk, cin, cout);
     const cudaStream_t user = static_cast<cudaStream_t>(stream);

@@ -576,6 +576,16 @@ void HostPipeline::release()
     capacity = 0;
 }
 
+void Network::claimDevice()
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) throw cuda_error("cudaGetDevice failed");
+    if (ownedDevice < 0) ownedDevice = dev;
+    else if (ownedDevice != dev)
+        throw std::runtime_error(format("this network keeps staging buffers on device %d and cannot run this call on device %d; "
+                                        "create one network object per device", ownedDevice, dev));
+}
+
 int64_t Network::gridTableBytes() const
 {
     int64_t b = 0;

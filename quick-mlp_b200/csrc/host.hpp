@@ -248,6 +248,8 @@ public:
     int64_t planeCapacity = 0;        // points per chunk
     bool planesUnsupported = false;   // the spec has no instantiation of the plane kernels
     HostPipeline hostPipeline;
+    int ownedDevice = -1;             // device the library-owned buffers above live on (-1: none allocated yet)
+    void claimDevice();               // first call: remember the current device; later calls: it must be the same
 
     BoundTensor paramInference, paramGradients;
     std::vector<qmlp_encoding*> encodingHandles; // owned wrappers handed out through the C ABI

@@ -776,25 +776,36 @@ __device__ __forceinline__ void wgrad_layer(const LaunchArgs& p, unsigned char* 
         __syncthreads();
         const __half* d = sDbase + buf * WG_SLAB * DS;
         const __half* a = sAbase + buf * WG_SLAB * BS;
+        // B fragment (k = point, n = cin) of column block nb: transposing ldmatrix of the (point, cin) tile, then
+        // a_{l-1} = Act_{l-1}(stashed pre-activation) on it
+        auto load_b = [&](int ks, int nb, uint32_t (&bf)[4]) {
+            ldmatrix_x4_trans(bf, smem_u32(a + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * BS + nb * 16 + (lane >> 4) * 8));
+            if constexpr (L > 0) {
+                using ActPrev = typename Spec::template Act<(L > 0 ? L - 1 : 0)>;
+#pragma unroll
+                for (int e = 0; e < 4; ++e)   // a register pairs two points of channel nb*16 + (e>>1)*8 + lane/4
+                    bf[e] = h2_as_u32(act_forward2_same_channel<ActPrev>(u32_as_h2(bf[e]), nb * 16 + (e >> 1) * 8 + (lane >> 2)));
+            }
+        };
+        // When the warps-across-blocks count is a multiple of the column blocks, all blocks of a warp share one column
+        // block: its B fragment is loaded and activated once per k step instead of once per block (the activation is
+        // the expensive part: config 4 puts a sine in front of a 64-wide layer)
+        constexpr int NB = CIN / 16;
+        constexpr bool SAME_NB = (WB % NB == 0);
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ++ks) {
             if (ks % KW != wk) continue;
+            uint32_t bf[4];
+            if constexpr (SAME_NB) load_b(ks, wb % NB, bf);
 #pragma unroll
             for (int b = 0; b < PB; ++b) {
                 const int blk = wb + b * WB;
                 if (blk >= NBLK) continue;
-                const int mb = blk / (CIN / 16), nb = blk % (CIN / 16);
+                const int mb = blk / NB, nb = blk % NB;
                 // A fragment = delta^T (m = cout, k = point): transposing ldmatrix of the (point, cout) tile
-                uint32_t af[4], bf[4];
+                uint32_t af[4];
                 ldmatrix_x4_trans(af, smem_u32(d + (ks * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * DS + mb * 16 + ((lane >> 3) & 1) * 8));
-                // B fragment (k = point, n = cin): transposing ldmatrix of the (point, cin) tile
-                ldmatrix_x4_trans(bf, smem_u32(a + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * BS + nb * 16 + (lane >> 4) * 8));
-                if constexpr (L > 0) {
-                    using ActPrev = typename Spec::template Act<(L > 0 ? L - 1 : 0)>;
-#pragma unroll
-                    for (int e = 0; e < 4; ++e)   // a register pairs two points of channel nb*16 + (e>>1)*8 + lane/4
-                        bf[e] = h2_as_u32(act_forward2_same_channel<ActPrev>(u32_as_h2(bf[e]), nb * 16 + (e >> 1) * 8 + (lane >> 2)));
-                }
+                if constexpr (!SAME_NB) load_b(ks, nb, bf);
                 mma16816(acc[b][0], af, bf[0], bf[1]);
                 mma16816(acc[b][1], af, bf[2], bf[3]);
                 if constexpr (BIAS) {

@@ -149,6 +149,50 @@ class FusedTrainer:
         self.step_count += 1
         self.backend.update(self.step_count, 1.0)
 
+    # -- batches that live in host memory ---------------------------------------------------------------------------
+    def _staging(self, x: torch.Tensor, target: torch.Tensor):
+        st = getattr(self, "_host_staging", None)
+        if st is None or st["x"][0].shape != x.shape or st["t"][0].shape != target.shape:
+            st = {"x": [torch.empty(x.shape, dtype=torch.float32, device=self.device) for _ in range(2)],
+                  "t": [torch.empty(target.shape, dtype=torch.float32, device=self.device) for _ in range(2)],
+                  "ready": [torch.cuda.Event(), torch.cuda.Event()], "free": [torch.cuda.Event(), torch.cuda.Event()],
+                  "stream": torch.cuda.Stream(device=self.device), "slot": 0, "pending": None}
+            self._host_staging = st
+        return st
+
+    def _upload(self, st, slot, x, target):
+        """Queues the upload of a host batch into staging slot `slot` on the copy stream."""
+        copy = st["stream"]
+        copy.wait_event(st["free"][slot])           # the step that last read this slot has been queued and will finish first
+        with torch.cuda.stream(copy):
+            st["x"][slot].copy_(x, non_blocking=True)
+            st["t"][slot].copy_(target, non_blocking=True)
+            st["ready"][slot].record(copy)
+        st["pending"] = (slot, x.data_ptr(), target.data_ptr())
+
+    def step_host(self, x: torch.Tensor, target: torch.Tensor, next_batch=None, global_points: Optional[int] = None):
+        """One training step on a batch in (page-locked) host memory. ``next_batch`` = (x, target) of the following
+        call: its upload is queued on a copy stream before this step's kernels, so it crosses the host link while they
+        run, and the following ``step_host`` finds it on the device."""
+        assert x.device.type == "cpu" and target.device.type == "cpu"
+        st = self._staging(x, target)
+        main = torch.cuda.current_stream()
+        pending = st["pending"]
+        if pending is not None and pending[1:] == (x.data_ptr(), target.data_ptr()):
+            slot = pending[0]                       # prefetched by the previous call
+        else:
+            slot = st["slot"]
+            st["free"][slot].record(main)
+            self._upload(st, slot, x, target)
+        st["pending"] = None
+        main.wait_event(st["ready"][slot])
+        if next_batch is not None:
+            other = slot ^ 1
+            st["free"][other].record(main)          # everything queued so far (all earlier steps) precedes the overwrite
+            self._upload(st, other, next_batch[0], next_batch[1])
+        self.step(st["x"][slot], st["t"][slot], global_points)
+        st["slot"] = slot ^ 1
+
     def mean_loss(self, global_points: int, reset=True) -> float:
         """Mean squared error accumulated since the last reset (synchronises)."""
         dist, world = self._world()

@@ -85,3 +85,42 @@ def test_loss_decreases_on_config3_small():
         if step % 20 == 19:
             losses.append(tr.mean_loss(n * 20))
     assert losses[-1] < 0.5 * losses[0], losses
+
+
+def test_step_from_host_memory_with_prefetch():
+    """step_host (batch in page-locked host memory, the following batch uploaded on a copy stream while the step runs)
+    leaves exactly the parameters that step() leaves on the same batches; gradients come from atomic sums, so "exactly"
+    is up to their summation order."""
+    import torch
+    from qmlp import bindings
+    from qmlp.trainer import FusedTrainer
+    cfg = smooth_config3()
+    spec = oracle.parse_spec(cfg)
+    params = helpers.xavier_parameters(spec, cfg, bias_scale=0.05).astype(np.float32)
+    table = helpers.grid_tables(spec, scale=0.1)[0]
+    batches = []
+    for i in range(4):
+        x = helpers.uniform(11, 10 + i, (3000, 3))
+        batches.append((torch.from_numpy(x).pin_memory(), torch.from_numpy(_target(x)).pin_memory()))
+
+    def run(host):
+        tr = FusedTrainer(bindings.Network(json.dumps(cfg)), lr=1e-2)
+        tr.set_parameters(torch.from_numpy(params).cuda(), [torch.from_numpy(table).cuda()])
+        for i, (x, t) in enumerate(batches):
+            if host:
+                nxt = batches[i + 1] if i + 1 < len(batches) and i != 1 else None    # one step without a prefetch in between
+                tr.step_host(x, t, next_batch=nxt)
+            else:
+                tr.step(x.cuda(), t.cuda())
+        torch.cuda.synchronize()
+        return tr.master.cpu().numpy(), float(tr.loss_sum.item())
+
+    m_dev, l_dev = run(False)
+    m_host, l_host = run(True)
+    assert abs(l_dev - l_host) <= 1e-4 * max(1.0, abs(l_dev))
+    # Adam turns a gradient entry into a step of about lr whatever its size, so entries whose gradient is rounding noise
+    # (atomic sums in a different order) may move differently: nearly all entries agree closely, none by more than the
+    # four steps of lr = 1e-2 that were taken
+    diff = np.abs(m_host - m_dev)
+    assert float((diff > 2e-4 + 1e-3 * np.abs(m_dev)).mean()) < 0.01 and float(diff.max()) <= 4.1e-2
+    assert bindings.QuickMLP.device_status() == 0
