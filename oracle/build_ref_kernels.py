@@ -1,4 +1,5 @@
-"""GPU-side oracle: the reference's own fused inference kernel, built from the reference checkout.  TEST INFRASTRUCTURE.
+"""GPU-side oracle: the reference's own fused kernels (inference, backward, weight update), built from the reference
+checkout.  TEST INFRASTRUCTURE.
 
 The reference ships its fused network as CUDA *templates with holes* (src_cpp/include/qmlp/kernels/network_forward.cuh)
 that its host code fills per network and hands to NVRTC (FusedNetwork::compileInferenceKernel,
@@ -56,7 +57,9 @@ def generate(cfg, ref, kind="inference"):
     """Fills network_forward.cuh (kind "inference") or network_backward.cuh (kind "backward") for `cfg` and appends the
     launcher. Returns CUDA source text."""
     kdir = os.path.join(ref, "src_cpp", "include", "qmlp", "kernels")
-    with open(os.path.join(kdir, "network_forward.cuh" if kind == "inference" else "network_backward.cuh")) as f:
+    template = {"inference": "network_forward.cuh", "backward": "network_backward.cuh",
+                "wgrad": "network_weight_update_block.cuh"}[kind]
+    with open(os.path.join(kdir, template)) as f:
         code = f.read()
     encs = cfg["encodings"]
     layers = cfg["network"]
@@ -141,7 +144,7 @@ def generate(cfg, ref, kind="inference"):
     code = code.replace("$$CHANNELS_IN$$", str(geo[0]["cin"]))
     code = code.replace("$$CHANNELS_OUT$$", str(geo[-1]["cout"]))
     code = code.replace("$$HAS_INPUT_GRADIENTS$$", "true")
-    code = code.replace("$$CALL_ENCODINGS$$", "\n".join(calls if kind == "inference" else adj_calls))
+    code = code.replace("$$CALL_ENCODINGS$$", "\n".join(adj_calls if kind == "backward" else calls))
     code = code.replace("$$CALL_NETWORK_LAYERS$$", "\n".join(layer_calls if kind == "inference" else adj_layer_calls))
     import re
     left = re.findall(r"\$\$[A-Z_]+\$", code)
@@ -280,8 +283,70 @@ extern "C" int ref_backward(int numel, const float* input, const float* adjOutpu
 }
 """ % dict(np=num_parameters, nin=cfg["num_inputs"], noutp=geo[-1]["cout"], uploads="".join(upload_code),
            maxc=max_channels, stash=stash_off)
+    # weight update: one launch of WeightUpdateSingleBlockKernel per layer, a single thread block each
+    # (src_cpp/src/fused_network.cpp:876-995 for the kernel names and shared memory, :1081-1144 for the launches)
+    wgrad_calls = []
+    for li, g in enumerate(geo):
+        if li == 0:
+            kname = ("WeightUpdateSingleBlockKernel<float, OHatTmpLoader<%d>, InputLoader<%d> >"
+                     % (g["cout"] // 16, g["cin"] // 16))
+            b_arg = "in"
+        else:
+            kname = ("WeightUpdateSingleBlockKernel<float, OHatTmpLoader<%d>, HiddenLoader<%d, activations::%s> >"
+                     % (g["cout"] // 16, g["cin"] // 16, geo[li - 1]["act"]))
+            b_arg = "const_cast<half*>(static_cast<const half*>(fwdTmp)) + static_cast<ptrdiff_t>(%d) * numel32" % geo[li - 1]["stash"]
+        wgrad_calls.append("""
+    {
+        auto kernel = %(kname)s;
+        const int perWarpIn = 2 * 32 * (%(cin)d + %(cout)d), perWarpOut = 4 * %(cin)d * %(cout)d;
+        const int perWarp = perWarpIn > perWarpOut ? perWarpIn : perWarpOut;
+        int minGrid = 0, best = 0;
+        e = cudaOccupancyMaxPotentialBlockSize(&minGrid, &best, kernel, 0, 0);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        int block = best, smem = best / 32 * perWarp;
+        if (smem > static_cast<int>(props.sharedMemPerBlock)) {
+            const int warps = static_cast<int>(props.sharedMemPerBlock) / perWarp;
+            if (warps == 0) return -1;   // "Layer too large for block-wise weight update"
+            block = warps * 32;
+            smem = warps * perWarp;
+        }
+        if (launchInfo) { launchInfo[2 * %(li)d] = block; launchInfo[2 * %(li)d + 1] = smem; }
+        kernel<<<1, block, smem, 0>>>(numel, gradWeights + %(w)d,
+                                      static_cast<half*>(adjTmp) + static_cast<ptrdiff_t>(%(stash)d) * numel32, %(b_arg)s);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return static_cast<int>(e);
+    }""" % dict(kname=kname, cin=g["cin"], cout=g["cout"], li=li, w=g["w"], stash=g["stash"], b_arg=b_arg))
+    wgrad_launcher = """
+// ---- launcher (not reference code): the weight-update launches of FusedNetwork::adjoint ------------------------------
+#include <cstring>
+struct RefGrid { const float* table; float* grad; const int* levels; const float* boxMin; const float* boxInvSize; };
+
+extern "C" int ref_num_parameters() { return %(np)d; }
+extern "C" int ref_num_layers() { return %(nl)d; }
+
+// Weight gradients of every layer, accumulated into gradWeights (fp32, the flat parameter layout; biases untouched: the
+// reference has no bias gradient). adjTmp: delta of every layer, fwdTmp: pre-activations of every layer, both
+// (N32 x Cout_l) halfs per layer in layer order. launchInfo receives (block, shared memory) per layer.
+extern "C" int ref_weight_update(int numel, const float* input, float* gradWeights, const void* fwdTmp, void* adjTmp,
+                                 const RefGrid* grids, int* launchInfo)
+{
+    using namespace qmlp::kernel;
+    cudaError_t e = cudaSuccess;
+    %(uploads)s
+    cudaDeviceProp props;
+    e = cudaGetDeviceProperties(&props, 0);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    const ptrdiff_t numel32 = (numel + 31) / 32 * 32;
+    const int sizesIn[2] = {numel, %(nin)d}, stridesIn[2] = {%(nin)d, 1};
+    Tensor2Read<float> in(const_cast<float*>(input), sizesIn, stridesIn);
+    %(calls)s
+    e = cudaDeviceSynchronize();
+    return static_cast<int>(e);
+}
+""" % dict(np=num_parameters, nl=len(geo), nin=cfg["num_inputs"], uploads="".join(upload_code), calls="".join(wgrad_calls))
     # tensor.cuh uses std::begin / std::copy and relies on its includer for <iterator>
-    return "#include <iterator>\n#include <algorithm>\n#include <cstdint>\n" + code + (launcher if kind == "inference" else backward_launcher)
+    tail = {"inference": launcher, "backward": backward_launcher, "wgrad": wgrad_launcher}[kind]
+    return "#include <iterator>\n#include <algorithm>\n#include <cstdint>\n#include <cstddef>\n" + code + tail
 
 
 def build(cfg, force=False, kind="inference"):
@@ -327,6 +392,7 @@ def build_all():
         built[name] = build(cfg)
         if name in BACKWARD_CONFIGS:
             built[name + " (backward)"] = build(cfg, kind="backward")
+            built[name + " (weight update)"] = build(cfg, kind="wgrad")
     return built
 
 

@@ -108,3 +108,37 @@ class ReferenceBackward:
             raise RuntimeError("reference backward kernel failed with CUDA error %d" % err)
         self.launch_info = tuple(info)
         return adj_input, deltas
+
+
+class ReferenceWeightUpdate:
+    """The reference's WeightUpdateSingleBlockKernel, one launch per layer in a single thread block each
+    (src_cpp/include/qmlp/kernels/network_weight_update_block.cuh:356-494, launched as FusedNetwork::adjoint does,
+    src_cpp/src/fused_network.cpp:1081-1144). Weight matrices only: the reference has no bias gradient."""
+
+    def __init__(self, cfg):
+        path = build_ref_kernels.build(cfg, kind="wgrad")
+        if path is None:
+            raise FileNotFoundError("the reference weight-update kernel for this configuration has not been built")
+        self.lib = C.CDLL(path)
+        self.lib.ref_weight_update.restype = C.c_int
+        self.lib.ref_weight_update.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(_RefGrid),
+                                               C.POINTER(C.c_int)]
+        self.spec = oracle.parse_spec(cfg)
+        assert self.lib.ref_num_parameters() == self.spec.num_parameters
+        assert self.lib.ref_num_layers() == len(self.spec.layers)
+        self.launch_info = None
+
+    def __call__(self, x, pre_activations, deltas, tables):
+        """x (N, Cin) fp32; pre_activations / deltas: fp16 CUDA tensors, (N32, Cout_l) row-major per layer in layer
+        order. Returns the fp32 gradient vector in the flat parameter layout (bias entries zero)."""
+        import torch
+        n = x.shape[0]
+        grads = torch.zeros((self.spec.num_parameters,), dtype=torch.float32, device=x.device)
+        arr, keep = _grid_array(self.spec, tables)
+        info = (C.c_int * (2 * len(self.spec.layers)))()
+        torch.cuda.synchronize()
+        err = self.lib.ref_weight_update(n, x.data_ptr(), grads.data_ptr(), pre_activations.data_ptr(), deltas.data_ptr(), arr, info)
+        if err != 0:
+            raise RuntimeError("reference weight-update kernel failed with error %d" % err)
+        self.launch_info = tuple(info)
+        return grads

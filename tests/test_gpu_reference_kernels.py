@@ -151,3 +151,21 @@ def test_backward_matches_reference_kernel(name):
             a, b = g.cpu().numpy(), r.cpu().numpy()
             assert float(np.abs(b).max()) > 0
             helpers.assert_close(a, b, f"{name}: table gradient", rtol=1e-2, atol=2e-3 * float(np.abs(b).max()), max_violations=0.01)
+
+    # weight gradients: the reference's single-block weight-update kernels on THIS build's stash and deltas against this
+    # build's split-batch kernel (same inputs on both sides, fp32 accumulation on both sides). The reference has no bias
+    # gradient, so only the weight matrices are compared.
+    import ref_kernels
+    try:
+        ref_wu = ref_kernels.ReferenceWeightUpdate(cfg)
+    except FileNotFoundError:
+        pytest.skip("reference kernels were not built (no reference checkout at build time)")
+    deltas = bwd[: n32 * stash_halfs]
+    ref_grads = ref_wu(tx, pre, deltas, tt).cpu().numpy()
+    mine = grads.cpu().numpy()
+    for li, l in enumerate(spec.layers):
+        a = mine[l.weights_start:l.weights_start + l.channels_in * l.channels_out]
+        b = ref_grads[l.weights_start:l.weights_start + l.channels_in * l.channels_out]
+        assert float(np.abs(b).max()) > 0
+        helpers.assert_close(a, b, f"{name}: weight gradient of layer {li}", rtol=2e-3, atol=1e-3 * float(np.abs(b).max()),
+                             max_violations=0.002)
