@@ -245,10 +245,33 @@ def reference_gpu_kernel(key, cfg, spec, params, tables, w):
     ref(x, tp, tt, 3)
     _, ms = ref(x, tp, tt, 10)
     grid, block, smem = ref.launch_info
-    return {"value": n / (ms * 1e-3), "unit": "points/s", "ms_per_launch": ms, "points": n,
-            "kind": "reference CUDA kernel template (wmma, half accumulation, fp32 tables) compiled for sm_100a; "
-                    "inference only" + ("; forward pass of the training workload" if w["mode"] == "train" else ""),
-            "launch": {"grid": grid, "block": block, "dynamic_smem": smem}}
+    out = {"value": n / (ms * 1e-3), "unit": "points/s", "ms_per_launch": ms, "points": n,
+           "kind": "reference CUDA kernel template (wmma, half accumulation, fp32 tables) compiled for sm_100a; "
+                   "inference only" + ("; forward pass of the training workload" if w["mode"] == "train" else ""),
+           "launch": {"grid": grid, "block": block, "dynamic_smem": smem}}
+    if w["mode"] == "train":
+        # The rest of a training step from the reference's kernels: backward (delta chain, table-gradient atomics) and
+        # the per-layer single-block weight update, timed on random stash contents of the right shapes (their timing
+        # does not depend on the values). No loss, no optimiser, no bias gradients: the reference has none.
+        try:
+            rb, rw = ref_kernels.ReferenceBackward(cfg), ref_kernels.ReferenceWeightUpdate(cfg)
+            n32 = (n + 31) // 32 * 32
+            pre = torch.randn((n32 * rb.stash_halfs,), device=dev, dtype=torch.float16)
+            adj = torch.randn((n, spec.num_outputs), device=dev)
+            grads = [torch.zeros_like(t) if t is not None else None for t in tt]
+            rb(x, adj, tp, pre, tt, grads)
+            _, deltas = rb(x, adj, tp, pre, tt, grads)
+            bwd_ms = rb.last_ms
+            rw(x, pre, deltas, tt)
+            wu_ms = rw.last_ms
+            out["training_step_kernels"] = {
+                "forward_ms": ms, "backward_ms": bwd_ms, "weight_update_ms": wu_ms,
+                "value": n / ((ms + bwd_ms + wu_ms) * 1e-3), "unit": "points/s",
+                "note": "forward (without stash) + backward + single-block weight update per layer; no loss, optimiser or "
+                        "bias gradient exists in the reference"}
+        except Exception as exc:   # not built for this configuration
+            out["training_step_kernels"] = {"unavailable": str(exc)[:200]}
+    return out
 
 
 # ----------------------------------------------------------------------------------------------------------------------

@@ -247,7 +247,7 @@ extern "C" int ref_stash_halfs_per_point() { return %(stash)d; }
 // adjOutput must be (N x %(noutp)d), i.e. zero-padded to the padded output width: the kernel reads that many columns
 // of every row whatever the tensor's width (network_backward.cuh:66-72).
 extern "C" int ref_backward(int numel, const float* input, const float* adjOutput, float* adjInput, const void* parameters,
-                            const void* fwdTmp, void* adjTmp, const RefGrid* grids, int* launchInfo)
+                            const void* fwdTmp, void* adjTmp, const RefGrid* grids, int* launchInfo, float* ms)
 {
     using namespace qmlp::kernel;
     cudaError_t e = cudaSuccess;
@@ -275,10 +275,20 @@ extern "C" int ref_backward(int numel, const float* input, const float* adjOutpu
     Tensor2Read<float> in(const_cast<float*>(input), sizesIn, stridesIn);
     Tensor2Read<float> adjOut(const_cast<float*>(adjOutput), sizesOut, stridesOut);
     Tensor2RW<float> adjIn(adjInput, sizesIn, stridesIn);
+    cudaEvent_t t0, t1;
+    cudaEventCreate(&t0);
+    cudaEventCreate(&t1);
+    cudaEventRecord(t0, 0);
     NetworkKernelBackward<<<grid, block, smem, 0>>>(numel, in, adjOut, adjIn, static_cast<const half*>(parameters),
                                                     static_cast<const half*>(fwdTmp), static_cast<half*>(adjTmp));
+    cudaEventRecord(t1, 0);
     e = cudaGetLastError();
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    float total = 0.f;
+    if (e == cudaSuccess) cudaEventElapsedTime(&total, t0, t1);
+    if (ms) *ms = total;
+    cudaEventDestroy(t0);
+    cudaEventDestroy(t1);
     return static_cast<int>(e);
 }
 """ % dict(np=num_parameters, nin=cfg["num_inputs"], noutp=geo[-1]["cout"], uploads="".join(upload_code),
@@ -328,7 +338,7 @@ extern "C" int ref_num_layers() { return %(nl)d; }
 // reference has no bias gradient). adjTmp: delta of every layer, fwdTmp: pre-activations of every layer, both
 // (N32 x Cout_l) halfs per layer in layer order. launchInfo receives (block, shared memory) per layer.
 extern "C" int ref_weight_update(int numel, const float* input, float* gradWeights, const void* fwdTmp, void* adjTmp,
-                                 const RefGrid* grids, int* launchInfo)
+                                 const RefGrid* grids, int* launchInfo, float* ms)
 {
     using namespace qmlp::kernel;
     cudaError_t e = cudaSuccess;
@@ -339,8 +349,18 @@ extern "C" int ref_weight_update(int numel, const float* input, float* gradWeigh
     const ptrdiff_t numel32 = (numel + 31) / 32 * 32;
     const int sizesIn[2] = {numel, %(nin)d}, stridesIn[2] = {%(nin)d, 1};
     Tensor2Read<float> in(const_cast<float*>(input), sizesIn, stridesIn);
+    cudaEvent_t t0, t1;
+    cudaEventCreate(&t0);
+    cudaEventCreate(&t1);
+    cudaEventRecord(t0, 0);
     %(calls)s
+    cudaEventRecord(t1, 0);
     e = cudaDeviceSynchronize();
+    float total = 0.f;
+    if (e == cudaSuccess) cudaEventElapsedTime(&total, t0, t1);
+    if (ms) *ms = total;
+    cudaEventDestroy(t0);
+    cudaEventDestroy(t1);
     return static_cast<int>(e);
 }
 """ % dict(np=num_parameters, nl=len(geo), nin=cfg["num_inputs"], uploads="".join(upload_code), calls="".join(wgrad_calls))
@@ -383,7 +403,7 @@ def default_configs():
             "config4": specs.config4(), "config5_small": specs.config5(log2_hashmap_size=12), "config5": specs.config5()}
 
 
-BACKWARD_CONFIGS = ("config1", "config2", "config3_small")
+BACKWARD_CONFIGS = ("config1", "config2", "config3_small", "config3", "config4")
 
 
 def build_all():

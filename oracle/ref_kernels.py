@@ -79,7 +79,8 @@ class ReferenceBackward:
         self.lib = C.CDLL(path)
         self.lib.ref_backward.restype = C.c_int
         self.lib.ref_backward.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
-                                          C.POINTER(_RefGrid), C.POINTER(C.c_int)]
+                                          C.POINTER(_RefGrid), C.POINTER(C.c_int), C.POINTER(C.c_float)]
+        self.last_ms = 0.0
         self.spec = oracle.parse_spec(cfg)
         assert self.lib.ref_num_parameters() == self.spec.num_parameters
         self.stash_halfs = self.lib.ref_stash_halfs_per_point()
@@ -102,8 +103,10 @@ class ReferenceBackward:
         arr, keep = _grid_array(self.spec, tables, table_grads)
         info = (C.c_int * 3)()
         torch.cuda.synchronize()
+        ms = C.c_float(0)
         err = self.lib.ref_backward(n, x.data_ptr(), adj_padded.data_ptr(), adj_input.data_ptr(), params_half.data_ptr(),
-                                    pre_activations.data_ptr(), deltas.data_ptr(), arr, info)
+                                    pre_activations.data_ptr(), deltas.data_ptr(), arr, info, C.byref(ms))
+        self.last_ms = float(ms.value)
         if err != 0:
             raise RuntimeError("reference backward kernel failed with CUDA error %d" % err)
         self.launch_info = tuple(info)
@@ -122,7 +125,8 @@ class ReferenceWeightUpdate:
         self.lib = C.CDLL(path)
         self.lib.ref_weight_update.restype = C.c_int
         self.lib.ref_weight_update.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(_RefGrid),
-                                               C.POINTER(C.c_int)]
+                                               C.POINTER(C.c_int), C.POINTER(C.c_float)]
+        self.last_ms = 0.0
         self.spec = oracle.parse_spec(cfg)
         assert self.lib.ref_num_parameters() == self.spec.num_parameters
         assert self.lib.ref_num_layers() == len(self.spec.layers)
@@ -137,7 +141,10 @@ class ReferenceWeightUpdate:
         arr, keep = _grid_array(self.spec, tables)
         info = (C.c_int * (2 * len(self.spec.layers)))()
         torch.cuda.synchronize()
-        err = self.lib.ref_weight_update(n, x.data_ptr(), grads.data_ptr(), pre_activations.data_ptr(), deltas.data_ptr(), arr, info)
+        ms = C.c_float(0)
+        err = self.lib.ref_weight_update(n, x.data_ptr(), grads.data_ptr(), pre_activations.data_ptr(), deltas.data_ptr(), arr, info,
+                                         C.byref(ms))
+        self.last_ms = float(ms.value)
         if err != 0:
             raise RuntimeError("reference weight-update kernel failed with error %d" % err)
         self.launch_info = tuple(info)
