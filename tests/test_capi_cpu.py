@@ -137,3 +137,42 @@ def test_simulated_network_and_weight_copy_are_plain_torch():
     y = net(torch.zeros((5, 4)))
     assert y.shape == (5, 2) and net.num_layers() == 2 and net.has_bias(0)
     assert net.get_weight(0, False, False).shape == (8, 4)
+
+
+def test_line_integration_and_per_channel_host_side(tmp_path):
+    """Host side of the two spec features the reference declares but cannot instantiate in a fused network: a
+    LineIntegration encoding (parse, sizes, JSON round trip, errors of src_cpp/src/encoding_line_integration.cpp:18-49)
+    and per-channel activation arrays (generated functor)."""
+    from qmlp import bindings
+    from qmlp._capi import QmlpError, ConfigurationError
+    line = {"id": "LineIntegration", "start_in": 2, "n_in": 3, "stepsize": 0.05, "blending": "average",
+            "volume": specs.hashgrid(3, 4, 2, 10, 4, 32)}
+    enc = bindings.Encoding(json.dumps(line))
+    grid = bindings.Encoding(json.dumps(specs.hashgrid(3, 4, 2, 10, 4, 32)))
+    assert enc.max_input_channel() == 2 + 6 - 1 and enc.num_output_channels() == 8 and enc.has_parameters()
+    assert enc.parameter_count() == grid.parameter_count() and enc.grid_levels() == grid.grid_levels()
+    back = json.loads(enc.to_json())
+    assert back["id"] == "LineIntegration" and back["volume"]["id"] == "HashGrid" and back["volume"]["start_in"] == 0
+    assert back["blending"] == "average" and abs(back["stepsize"] - 0.05) < 1e-6
+    assert json.loads(bindings.Encoding(enc.to_json()).to_json()) == back
+    for bad in ({"stepsize": 0.0}, {"n_in": 2}, {"volume": {"id": "Identity", "start_in": 0, "n_in": 3}}):
+        with pytest.raises(QmlpError):
+            bindings.Encoding(json.dumps(dict(line, **bad)))
+    with pytest.raises(QmlpError):
+        bindings.Encoding(json.dumps({k: v for k, v in line.items() if k != "blending"}))
+
+    old = bindings.QuickMLP.kernel_cache_dir()
+    bindings.QuickMLP.set_kernel_cache_dir(str(tmp_path))
+    try:
+        cfg = {"num_inputs": 8, "num_outputs": 2, "activation_specification": specs.BUILTIN, "encodings": [line],
+               "network": specs.mlp([16, 2], [["relu"] * 6 + ["sine"] * 10, "identity"], True)}
+        bindings.Network(json.dumps(cfg)).compile(0)
+        src = open(os.path.join(tmp_path, [f for f in os.listdir(tmp_path) if f.endswith(".cu")][0])).read()
+        assert "EncLine<2, 3, 4, 2, true, 0, 0, false, true>" in src and "HAS_LINE = true" in src
+        assert "struct PerChannelAct0 : PerChannelActivation<PerChannelAct0>" in src
+        assert "if (c < 6) return BuiltinRelu::forward(x);" in src and "if (c < 16) return BuiltinSine::forward(x);" in src
+    finally:
+        bindings.QuickMLP.set_kernel_cache_dir(old)
+    with pytest.raises(QmlpError):
+        bindings.QuickMLP.set_kernel_path(4)
+    bindings.QuickMLP.set_kernel_path(0)
