@@ -82,7 +82,8 @@ QMLP_API int qmlp_set_kernel_include_dir(const char* dir);
 
 /* Kernel family used for fused inference: 0 = the best one instantiated for the spec and the batch (tcgen05 tensor-core
  * kernel when the layer widths allow it and the batch fills its tile slots, else the mma.sync kernel; a level-major
- * encoding pass in front of the tcgen05 kernel when the grid tables are much larger than L2,
+ * encoding pass in front of the tcgen05 kernel when the grid tables are much larger than L2 or when a large batch
+ * (2^18 points or more) fetches 96 or more table rows per point,
  * which makes the network keep a feature buffer of up to 2^22 points and 512 MB from its first such call until it is
  * destroyed), 1 = the mma.sync kernels only, 2 = the level-major pass for every grid network, 3 = the tcgen05 kernel at
  * any batch size. Takes the place of the

@@ -325,11 +325,15 @@ static void inferenceLocked(Network& n, const qmlp_tensor_t* input, qmlp_tensor_
     a.output = static_cast<float*>(output->data);
     a.outS0 = output->strides[0];
     a.outS1 = output->strides[1];
-    // Tables much larger than L2: encode level by level into planes, chunk by chunk, then run the layer chain on the
-    // planes (kernels/grid_planes.cuh). kernelPath 2 forces this path for any grid network.
+    // Encode level by level into planes, chunk by chunk, then run the layer chain on the planes
+    // (kernels/grid_planes.cuh): when the tables are much larger than L2 (the level in work stays L2-resident), and when
+    // the gather dominates a large batch (96 or more table rows per point: the dedicated pass keeps four light CTAs per
+    // SM on nothing but gathers and runs at the SM's L2-request rate; config 3 at 2^20 points 0.40 -> 0.34 ms, while
+    // config 4 with 72 rows per point and a heavier layer chain is level). kernelPath 2 forces this path.
     const int path = Library::instance().kernelPath;
+    const bool gatherBound = n.gathersPerPoint() >= 96 && a.numel >= (1 << 18);
     const bool wantPlanes = !n.planesUnsupported && a.numGrids > 0 && a.numel > 0 &&
-                            (path == 2 || (path == 0 && n.gridTableBytes() > (96ll << 20)));
+                            (path == 2 || (path == 0 && (n.gridTableBytes() > (96ll << 20) || gatherBound)));
     if (wantPlanes) {
         // Chunk: as many points as fit in 512 MB of planes, at most 2^22. A level's table is fetched from HBM once per
         // chunk, so large chunks amortise it; the planes themselves are streamed (written once, read once).

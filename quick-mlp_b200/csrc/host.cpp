@@ -586,6 +586,15 @@ void Network::claimDevice()
                                         "create one network object per device", ownedDevice, dev));
 }
 
+int Network::gathersPerPoint() const
+{
+    int g = 0;
+    for (const auto& e : encodings_)
+        if (auto* h = dynamic_cast<const EncodingHashGrid*>(e.get()))
+            if (!h->isLine()) g += static_cast<int>(h->levelTable().size()) << h->dimension();
+    return g;
+}
+
 int64_t Network::gridTableBytes() const
 {
     int64_t b = 0;

@@ -161,6 +161,7 @@ public:
     void fillGrid(kernel::GridP& g) const override;
     const std::vector<GridLevel>& levelTable() const { return table_; }
     int features() const { return features_; }
+    int dimension() const { return dim_; }
     Json gridJson() const;   // the hash grid's own configuration (id "HashGrid")
 
 protected:
@@ -242,6 +243,7 @@ public:
 
     ~Network();
     int64_t gridTableBytes() const;   // bytes of all bound grid tables (what the gather walks through)
+    int gathersPerPoint() const;      // table rows fetched per point by all plain grid encodings: sum of levels * 2^D
     // level-major encoding pass (inference of networks with tables larger than L2): chunk buffer, allocated at the
     // first such call and kept until the network is destroyed
     void* planes = nullptr;

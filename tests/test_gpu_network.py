@@ -150,7 +150,7 @@ def test_level_major_encoding_pass(name, half_tables):
     try:
         bindings.QuickMLP.set_kernel_path(2)
         out_planes = net.inference(x, t_params, tabs)
-        bindings.QuickMLP.set_kernel_path(0)
+        bindings.QuickMLP.set_kernel_path(3)     # gather fused into the layer kernel (automatic choice may pick the pass)
         out_fused = net.inference(x, t_params, tabs)
     finally:
         bindings.QuickMLP.set_kernel_path(0)
