@@ -913,16 +913,41 @@ int qmlp_trainer_gradients_part(qmlp_trainer_t* tr, const qmlp_tensor_t* input, 
     a.tS1 = target->strides[1];
     a.lossScale = static_cast<float>(2.0 / (static_cast<double>(global_points) * n.channelsOut()));
     a.lossSum = loss_sum;
-    if (parts & 1) launchNet(n, kernel::KERNEL_FORWARD_LOSS, a, stream);
+    bool anyGrid = false;
+    for (int i = 0; i < n.numEncodings(); ++i) anyGrid = anyGrid || n.encoding(i)->hasParameters();
+    size_t pb = b + static_cast<size_t>(n32) * n.channelsOut() * 4;
+    pb = (pb + 255) / 256 * 256;
+    __half* planes = anyGrid ? reinterpret_cast<__half*>(ws + pb) : nullptr;
+    if (parts & 1) {
+        // Gather-dominated batches (same rule as inference): the encodings are computed one grid level at a time into
+        // the plane region of the workspace, which is free until the backward kernel writes the adjoint planes there,
+        // and the forward kernel reads its layer-0 operand from the planes.
+        const int path = Library::instance().kernelPath;
+        const bool wantPlanes = planes != nullptr && !n.planesUnsupported && a.numGrids > 0 && numel > 0 &&
+                                (path == 2 || (path == 0 && n.gathersPerPoint() >= 96 && numel >= (1 << 18)));
+        bool done = false;
+        if (wantPlanes) {
+            a.planes = planes;
+            a.planeStride = n32;
+            auto m = n.module(n.currentHalfMask());
+            int launches = 0;
+            const int e = m->launch(kernel::KERNEL_ENCODE_PLANES, &a, static_cast<cudaStream_t>(stream), &launches);
+            if (e == static_cast<int>(cudaErrorNotSupported)) {
+                n.planesUnsupported = true;
+            } else {
+                checkLaunch(e, "kernel launch failed");
+                n.launchCount += launches;
+                launchNet(n, kernel::KERNEL_FORWARD_LOSS_PLANES, a, stream);
+                done = true;
+            }
+        }
+        if (!done) launchNet(n, kernel::KERNEL_FORWARD_LOSS, a, stream);
+    }
     a.adjOutput = adjOut;
     a.aoS0 = n.channelsOut();
     a.aoS1 = 1;
-    bool anyGrid = false;
-    for (int i = 0; i < n.numEncodings(); ++i) anyGrid = anyGrid || n.encoding(i)->hasParameters();
     a.flags = kernel::FLAG_GRAD_WEIGHTS | (anyGrid ? kernel::FLAG_GRAD_ENCODINGS : 0);
-    size_t pb = b + static_cast<size_t>(n32) * n.channelsOut() * 4;
-    pb = (pb + 255) / 256 * 256;
-    if (parts & 1) launchBackward(n, a, anyGrid ? reinterpret_cast<__half*>(ws + pb) : nullptr, n32, stream);
+    if (parts & 1) launchBackward(n, a, planes, n32, stream);
     if (parts & 2) launchNet(n, kernel::KERNEL_WGRAD, a, stream);
     QMLP_CATCH
 }

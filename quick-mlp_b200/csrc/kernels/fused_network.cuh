@@ -289,6 +289,75 @@ __device__ __forceinline__ void encode_point(const LaunchArgs& p, const RowReade
     }
 }
 
+// ---- layer-0 operand from level-major feature planes ---------------------------------------------------------------
+// (written by encode_planes_kernel, kernels/grid_planes.cuh: plane of channel c = planes + planeStride * c, F halfs per
+// point for the F channels of one grid level, N halfs per point for an identity encoding)
+struct HalfRowPlaneWriter { // one row of the warp's shared-memory tile, fed with halfs
+    __half* row;
+    __device__ __forceinline__ void half(int c, __half v) const { row[c] = v; }
+    __device__ __forceinline__ void half2(int c, uint32_t v) const { *reinterpret_cast<uint32_t*>(row + c) = v; }
+};
+
+// layer-0 operand row of one point from the planes (Out writes halfs: out.half(channel, value)).
+// All plane values of an encoding are fetched into registers before the first one is written: the writes go to shared
+// memory through a generic pointer, so a load placed after a write could not be moved above it, and the 16 loads of
+// configuration 5 would run one memory latency after the other (measured: 22 700 cycles per tile instead of ~5 000).
+template <class Spec, int E, class Out>
+__device__ __forceinline__ void read_planes_point(const LaunchArgs& p, long long local, const Out& out)
+{
+    if constexpr (E < Spec::NUM_ENCODINGS) {
+        using Enc = typename Spec::template Enc<E>;
+        if constexpr (!Enc::IS_GRID) {
+            const __half* src = p.planes + p.planeStride * Enc::OUT_OFF + local * Enc::N;
+            __half v[Enc::N];
+#pragma unroll
+            for (int i = 0; i < Enc::N; ++i) v[i] = __ldg(src + i);
+#pragma unroll
+            for (int i = 0; i < Enc::N; ++i) out.half(Enc::OUT_OFF + i, v[i]);
+        } else {
+            constexpr int GROUPS = Enc::CONCAT ? Enc::L : 1;
+            constexpr int F = Enc::F;
+            const __half* base = p.planes + p.planeStride * Enc::OUT_OFF + local * F;
+            if constexpr (F == 2) {
+                uint32_t v[GROUPS];
+#pragma unroll
+                for (int l = 0; l < GROUPS; ++l) v[l] = ldg_nc_u32(base + p.planeStride * (l * F));
+#pragma unroll
+                for (int l = 0; l < GROUPS; ++l) out.half2(Enc::OUT_OFF + l * F, v[l]);
+            } else if constexpr (F == 4) {
+                uint2 v[GROUPS];
+#pragma unroll
+                for (int l = 0; l < GROUPS; ++l) v[l] = ldg_nc_u64(base + p.planeStride * (l * F));
+#pragma unroll
+                for (int l = 0; l < GROUPS; ++l) {
+                    out.half2(Enc::OUT_OFF + l * F, v[l].x);
+                    out.half2(Enc::OUT_OFF + l * F + 2, v[l].y);
+                }
+            } else if constexpr (F == 8) {
+                uint4 v[GROUPS];
+#pragma unroll
+                for (int l = 0; l < GROUPS; ++l) v[l] = ldg_nc_u128(base + p.planeStride * (l * F));
+#pragma unroll
+                for (int l = 0; l < GROUPS; ++l) {
+                    out.half2(Enc::OUT_OFF + l * F, v[l].x);
+                    out.half2(Enc::OUT_OFF + l * F + 2, v[l].y);
+                    out.half2(Enc::OUT_OFF + l * F + 4, v[l].z);
+                    out.half2(Enc::OUT_OFF + l * F + 6, v[l].w);
+                }
+            } else {
+                __half v[GROUPS * F];
+#pragma unroll
+                for (int l = 0; l < GROUPS; ++l)
+#pragma unroll
+                    for (int i = 0; i < F; ++i) v[l * F + i] = __ldg(base + p.planeStride * (l * F) + i);
+#pragma unroll
+                for (int i = 0; i < GROUPS * F; ++i) out.half(Enc::OUT_OFF + i, v[i]);
+            }
+        }
+        read_planes_point<Spec, E + 1, Out>(p, local, out);
+    }
+}
+
 // ---- forward layer chain -------------------------------------------------------------------------------------
 // MODE 0: inference, 1: forward with stash, 2: forward with stash + L2 loss gradient instead of the output
 template <class Spec, int L, int MODE>
@@ -335,24 +404,36 @@ __device__ __forceinline__ void forward_layers(const LaunchArgs& p, const __half
         }
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
+            __half2 pre[2][2]; // [h][row r | row r + 8]
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                pre[h][0] = __floats2half2_rn(acc[m][h][0], acc[m][h][1]);
+                pre[h][1] = __floats2half2_rn(acc[m][h][2], acc[m][h][3]);
+                if constexpr (BIAS) {
+                    // the fp32 accumulator is rounded to half first, then the (half) bias is added
+                    const __half2 b2 = *reinterpret_cast<const __half2*>(bias + j * 16 + h * 8 + q * 2);
+                    pre[h][0] = __hadd2(pre[h][0], b2);
+                    pre[h][1] = __hadd2(pre[h][1], b2);
+                }
+            }
+            const long long row0 = rowBase + m * 16 + r;
+            if constexpr (MODE >= 1) {
+                // pre-activation stash, row-major (N32, COUT) per layer (reference: kernels/layer.cuh:156-163). Plain
+                // 4-byte stores: collecting 16-byte pieces inside the quad first (four shuffles per 16 x 16 block, here
+                // and in the backward kernel) halves the sectors touched but adds instructions to the load/store queue
+                // that the gathers and reductions already fill: measured 6 % (config 3) and 15 % (config 4) slower.
+                __half* st = p.fwdTmp + n32 * SL::preOffset(L);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int col = j * 16 + h * 8 + q * 2;
+                    if (row0 < p.numel) *reinterpret_cast<__half2*>(st + row0 * COUT + col) = pre[h][0];
+                    if (row0 + 8 < p.numel) *reinterpret_cast<__half2*>(st + (row0 + 8) * COUT + col) = pre[h][1];
+                }
+            }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const int col = j * 16 + h * 8 + q * 2;
-                __half2 lo = __floats2half2_rn(acc[m][h][0], acc[m][h][1]); // row r
-                __half2 hi = __floats2half2_rn(acc[m][h][2], acc[m][h][3]); // row r + 8
-                if constexpr (BIAS) {
-                    // the fp32 accumulator is rounded to half first, then the (half) bias is added
-                    const __half2 b2 = *reinterpret_cast<const __half2*>(bias + col);
-                    lo = __hadd2(lo, b2);
-                    hi = __hadd2(hi, b2);
-                }
-                const long long row0 = rowBase + m * 16 + r;
-                if constexpr (MODE >= 1) {
-                    // pre-activation stash, row-major (N32, COUT) per layer (reference: kernels/layer.cuh:156-163)
-                    __half* st = p.fwdTmp + n32 * SL::preOffset(L);
-                    if (row0 < p.numel) *reinterpret_cast<__half2*>(st + row0 * COUT + col) = lo;
-                    if (row0 + 8 < p.numel) *reinterpret_cast<__half2*>(st + (row0 + 8) * COUT + col) = hi;
-                }
+                const __half2 lo = pre[h][0], hi = pre[h][1];
                 const __half2 zlo = act_forward2<Act>(lo, col), zhi = act_forward2<Act>(hi, col);
                 if constexpr (!LAST) {
                     aOut[m][j][h * 2 + 0] = h2_as_u32(zlo);
@@ -365,7 +446,7 @@ __device__ __forceinline__ void forward_layers(const LaunchArgs& p, const __half
                     for (int e = 0; e < 4; ++e) {
                         const long long row = row0 + (e >> 1) * 8;
                         const int c = col + (e & 1);
-                        if (c < Spec::NUM_OUTPUTS && row < p.numel) {
+                        if (c < Spec::NUM_OUTPUTS && row < p.numel) { // the row is the same for the four lanes of a quad
                             if constexpr (MODE == 2) {
                                 const float d = v[e] - __ldg(p.target + row * p.tS0 + c * p.tS1);
                                 lossAcc += d * d;
@@ -382,10 +463,13 @@ __device__ __forceinline__ void forward_layers(const LaunchArgs& p, const __half
     if constexpr (!LAST) forward_layers<Spec, L + 1, MODE>(p, sW, sB, aOut, rowBase, n32, lossAcc);
 }
 
-template <class Spec, int MODE>
+// MODE_ bit 2 (value 4): the encodings were computed by encode_planes_kernel; layer 0 reads the feature planes
+template <class Spec, int MODE_>
 __global__ void __launch_bounds__(Spec::WARPS * 32, resident_ctas<Spec>())
 fused_forward_kernel(const __grid_constant__ LaunchArgs p)
 {
+    constexpr int MODE = MODE_ & 3;
+    constexpr bool FROM_PLANES = (MODE_ & 4) != 0;
     using SL = SmemLayout<Spec>;
     extern __shared__ __align__(16) unsigned char smem[];
     __half* sW = reinterpret_cast<__half*>(smem);
@@ -408,8 +492,12 @@ fused_forward_kernel(const __grid_constant__ LaunchArgs p)
         __half* row = tile + lane * TS;
         // encodings; padding channels and invalid tail points are zero (kernels/network_forward.cuh:67-89)
         if (myRow < p.numel) {
-            RowReader in{p.input + myRow * p.inS0, p.inS1};
-            encode_point<Spec, 0>(p, in, HalfRowWriter{row});
+            if constexpr (FROM_PLANES) {
+                read_planes_point<Spec, 0>(p, myRow, HalfRowPlaneWriter{row});
+            } else {
+                RowReader in{p.input + myRow * p.inS0, p.inS1};
+                encode_point<Spec, 0>(p, in, HalfRowWriter{row});
+            }
 #pragma unroll
             for (int c = Spec::ENC_CHANNELS; c < CIN0; ++c) row[c] = __ushort_as_half(0);
         } else {
@@ -999,6 +1087,10 @@ struct NetworkLaunchers {
             break;
         case KERNEL_FORWARD: e = forward<1>(a, s); break;
         case KERNEL_FORWARD_LOSS: e = forward<2>(a, s); break;
+        case KERNEL_FORWARD_LOSS_PLANES:
+            if constexpr (TcLayout<Spec>::eligible() && Spec::NUM_ENCODINGS > 0) e = forward<6>(a, s);
+            else e = cudaErrorNotSupported;
+            break;
         case KERNEL_BACKWARD: e = backward(a, s); n = (a.flags & 7) ? 1 : 0; break;
         case KERNEL_WGRAD: e = wgrad(a, s); break;
         case KERNEL_SCATTER_PLANES: e = PlaneLaunchers<Spec>::scatter(a, s); break;

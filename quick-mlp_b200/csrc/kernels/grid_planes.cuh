@@ -234,65 +234,5 @@ struct PlaneLaunchers {
     }
 };
 
-// layer-0 operand row of one point from the planes (Out writes halfs: out.half(channel, value)).
-// All plane values of an encoding are fetched into registers before the first one is written: the writes go to shared
-// memory through a generic pointer, so a load placed after a write could not be moved above it, and the 16 loads of
-// configuration 5 would run one memory latency after the other (measured: 22 700 cycles per tile instead of ~5 000).
-template <class Spec, int E, class Out>
-__device__ __forceinline__ void read_planes_point(const LaunchArgs& p, long long local, const Out& out)
-{
-    if constexpr (E < Spec::NUM_ENCODINGS) {
-        using Enc = typename Spec::template Enc<E>;
-        if constexpr (!Enc::IS_GRID) {
-            const __half* src = p.planes + p.planeStride * Enc::OUT_OFF + local * Enc::N;
-            __half v[Enc::N];
-#pragma unroll
-            for (int i = 0; i < Enc::N; ++i) v[i] = __ldg(src + i);
-#pragma unroll
-            for (int i = 0; i < Enc::N; ++i) out.half(Enc::OUT_OFF + i, v[i]);
-        } else {
-            constexpr int GROUPS = Enc::CONCAT ? Enc::L : 1;
-            constexpr int F = Enc::F;
-            const __half* base = p.planes + p.planeStride * Enc::OUT_OFF + local * F;
-            if constexpr (F == 2) {
-                uint32_t v[GROUPS];
-#pragma unroll
-                for (int l = 0; l < GROUPS; ++l) v[l] = ldg_nc_u32(base + p.planeStride * (l * F));
-#pragma unroll
-                for (int l = 0; l < GROUPS; ++l) out.half2(Enc::OUT_OFF + l * F, v[l]);
-            } else if constexpr (F == 4) {
-                uint2 v[GROUPS];
-#pragma unroll
-                for (int l = 0; l < GROUPS; ++l) v[l] = ldg_nc_u64(base + p.planeStride * (l * F));
-#pragma unroll
-                for (int l = 0; l < GROUPS; ++l) {
-                    out.half2(Enc::OUT_OFF + l * F, v[l].x);
-                    out.half2(Enc::OUT_OFF + l * F + 2, v[l].y);
-                }
-            } else if constexpr (F == 8) {
-                uint4 v[GROUPS];
-#pragma unroll
-                for (int l = 0; l < GROUPS; ++l) v[l] = ldg_nc_u128(base + p.planeStride * (l * F));
-#pragma unroll
-                for (int l = 0; l < GROUPS; ++l) {
-                    out.half2(Enc::OUT_OFF + l * F, v[l].x);
-                    out.half2(Enc::OUT_OFF + l * F + 2, v[l].y);
-                    out.half2(Enc::OUT_OFF + l * F + 4, v[l].z);
-                    out.half2(Enc::OUT_OFF + l * F + 6, v[l].w);
-                }
-            } else {
-                __half v[GROUPS * F];
-#pragma unroll
-                for (int l = 0; l < GROUPS; ++l)
-#pragma unroll
-                    for (int i = 0; i < F; ++i) v[l * F + i] = __ldg(base + p.planeStride * (l * F) + i);
-#pragma unroll
-                for (int i = 0; i < GROUPS * F; ++i) out.half(Enc::OUT_OFF + i, v[i]);
-            }
-        }
-        read_planes_point<Spec, E + 1, Out>(p, local, out);
-    }
-}
-
 } // namespace kernel
 } // namespace qmlp

@@ -79,7 +79,8 @@ enum KernelId {
     KERNEL_ACTIVATION_ADJOINT = 8,
     KERNEL_ENCODE_PLANES = 9,      // encodings of a chunk of points -> level-major feature planes
     KERNEL_INFERENCE_PLANES = 10,  // layer chain reading the feature planes instead of running the encodings
-    KERNEL_SCATTER_PLANES = 11     // adjoint feature planes -> grid table gradients, one grid level at a time
+    KERNEL_SCATTER_PLANES = 11,    // adjoint feature planes -> grid table gradients, one grid level at a time
+    KERNEL_FORWARD_LOSS_PLANES = 12 // KERNEL_FORWARD_LOSS with layer 0 fed from the planes of KERNEL_ENCODE_PLANES
 };
 
 // arguments of the stand-alone activation kernels

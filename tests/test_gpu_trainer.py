@@ -26,8 +26,19 @@ def smooth_config3(log2_hashmap_size=11):
     return cfg
 
 
+@pytest.fixture
+def kernel_path(request):
+    """Library-wide kernel path for one test (2: level-major encoding pass for every grid network, which the automatic
+    choice takes only for large gather-dominated batches), restored afterwards."""
+    from qmlp import bindings
+    bindings.QuickMLP.set_kernel_path(request.param)
+    yield request.param
+    bindings.QuickMLP.set_kernel_path(0)
+
+
+@pytest.mark.parametrize("kernel_path", [0, 2], indirect=True)
 @pytest.mark.parametrize("half_tables", [True, False])
-def test_training_steps_match_oracle(half_tables):
+def test_training_steps_match_oracle(half_tables, kernel_path):
     import torch
     from qmlp import bindings
     from qmlp.trainer import FusedTrainer
