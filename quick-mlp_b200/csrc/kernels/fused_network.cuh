@@ -767,7 +767,16 @@ template <class Spec>
 struct WgradSmem {
     __host__ __device__ static constexpr int maxCout() { int m = 0; for (int i = 0; i < Spec::NUM_LAYERS; ++i) m = Spec::COUT[i] > m ? Spec::COUT[i] : m; return m; }
     __host__ __device__ static constexpr int maxCin() { int m = 0; for (int i = 0; i < Spec::NUM_LAYERS; ++i) m = Spec::CIN[i] > m ? Spec::CIN[i] : m; return m; }
-    __host__ __device__ static constexpr int bytes() { return 2 * WG_SLAB * ((maxCout() + 8) + (maxCin() + 8)) * 2; }
+    __host__ __device__ static constexpr int stageBytes() { return WG_SLAB * ((maxCout() + 8) + (maxCin() + 8)) * 2; }
+    // Slabs in flight per CTA. The kernel does little work per byte, so what it reaches is set by how many bytes each
+    // SM keeps requested: with two buffers a CTA waits out one full memory latency per slab (config 4: 2.9 TB/s).
+    // As many stages as two CTAs per SM have shared memory for, at most four.
+    __host__ __device__ static constexpr int stages()
+    {
+        int st = (224 * 1024 / 2) / stageBytes();
+        return st > 4 ? 4 : (st < 2 ? 2 : st);
+    }
+    __host__ __device__ static constexpr int bytes() { return stages() * stageBytes(); }
 };
 
 // CTAs of the one-dimensional grid are dealt to the layers in proportion to the bytes a layer reads per point
@@ -819,8 +828,9 @@ __device__ __forceinline__ void wgrad_layer(const LaunchArgs& p, unsigned char* 
     constexpr int KSTEPS = WG_SLAB / 16;
     constexpr bool BIAS = Spec::BOFF[L] >= 0;
 
-    __half* const sDbase = reinterpret_cast<__half*>(smem);            // [2][WG_SLAB][DS]
-    __half* const sAbase = sDbase + 2 * WG_SLAB * DS;                    // [2][WG_SLAB][BS]
+    constexpr int ST = WgradSmem<Spec>::stages();
+    __half* const sDbase = reinterpret_cast<__half*>(smem);            // [ST][WG_SLAB][DS]
+    __half* const sAbase = sDbase + ST * WG_SLAB * DS;                   // [ST][WG_SLAB][BS]
 
     const long long n32 = (p.numel + 31) / 32 * 32;
     const __half* gD = p.adjTmp + n32 * SL::deltaOffset(L);
@@ -854,13 +864,17 @@ __device__ __forceinline__ void wgrad_layer(const LaunchArgs& p, unsigned char* 
 
     long long slab = cta;
     int buf = 0;
-    if (slab < numSlabs) load_slab(slab, 0);
-    cp_async_commit();
-    for (; slab < numSlabs; slab += ctas) {
-        const long long next = slab + ctas;
-        if (next < numSlabs) load_slab(next, buf ^ 1);
+#pragma unroll
+    for (int i = 0; i < ST - 1; ++i) {   // one commit group per slab, empty past the end
+        if (slab + static_cast<long long>(i) * ctas < numSlabs) load_slab(slab + static_cast<long long>(i) * ctas, i);
         cp_async_commit();
-        cp_async_wait<1>();
+    }
+    for (; slab < numSlabs; slab += ctas) {
+        // the buffer refilled here was read in the previous iteration, which ended with __syncthreads()
+        const long long next = slab + static_cast<long long>(ST - 1) * ctas;
+        if (next < numSlabs) load_slab(next, (buf + ST - 1) % ST);
+        cp_async_commit();
+        cp_async_wait<ST - 1>();
         __syncthreads();
         const __half* d = sDbase + buf * WG_SLAB * DS;
         const __half* a = sAbase + buf * WG_SLAB * BS;
@@ -902,7 +916,7 @@ __device__ __forceinline__ void wgrad_layer(const LaunchArgs& p, unsigned char* 
             }
         }
         __syncthreads();
-        buf ^= 1;
+        buf = (buf + 1) % ST;
     }
     cp_async_wait<0>();
 
