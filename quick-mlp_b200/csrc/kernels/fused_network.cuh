@@ -96,6 +96,18 @@ struct SmemLayout {
     }
 };
 
+// Layout of a pre-activation or delta matrix (N32 points x C channels, halfs) in the stash: tiles of 32 points, each
+// tile cut into blocks of 8 points x 8 channels that are stored contiguously (128 bytes, point-major), block (cb, rb) of
+// a tile at ((cb * 4 + rb) * 64) halfs. An m16n8k16 accumulator / A fragment register of a warp (lane = 4 * r + q holds
+// row r, columns 2 q and 2 q + 1 of an 8 x 8 block) then covers exactly one block, so the 4-byte accesses of a warp
+// are one contiguous 128-byte line: four sector requests instead of the eight half-filled ones a row-major matrix
+// costs. The forward and backward kernels are bound by the rate of such requests (one per clock and SM), and the stash
+// accounted for a third of them. A row of 8 channels is still one 16-byte piece, which is what wgrad_kernel copies.
+__host__ __device__ __forceinline__ long long stash_block(long long tileRow0, int channels, int rb, int cb)
+{
+    return tileRow0 * channels + (cb * 4 + rb) * 64;
+}
+
 // CTAs per SM the forward and backward kernels are compiled for: two (a 128-register budget per thread, which costs
 // the 128-wide networks a few dozen bytes of spills but doubles the warps that hide gather and stash latency) whenever
 // two copies of the shared-memory plan fit on an SM, else one.
@@ -418,16 +430,15 @@ __device__ __forceinline__ void forward_layers(const LaunchArgs& p, const __half
             }
             const long long row0 = rowBase + m * 16 + r;
             if constexpr (MODE >= 1) {
-                // pre-activation stash, row-major (N32, COUT) per layer (reference: kernels/layer.cuh:156-163). Plain
-                // 4-byte stores: collecting 16-byte pieces inside the quad first (four shuffles per 16 x 16 block, here
-                // and in the backward kernel) halves the sectors touched but adds instructions to the load/store queue
-                // that the gathers and reductions already fill: measured 6 % (config 3) and 15 % (config 4) slower.
-                __half* st = p.fwdTmp + n32 * SL::preOffset(L);
+                // pre-activation stash (N32, COUT) per layer (reference: kernels/layer.cuh:156-163) in 8 x 8 blocks
+                // (stash_block): a register of the warp is one 128-byte line
+                __half* st = p.fwdTmp + n32 * SL::preOffset(L) + (r * 8 + q * 2);
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const int col = j * 16 + h * 8 + q * 2;
-                    if (row0 < p.numel) *reinterpret_cast<__half2*>(st + row0 * COUT + col) = pre[h][0];
-                    if (row0 + 8 < p.numel) *reinterpret_cast<__half2*>(st + (row0 + 8) * COUT + col) = pre[h][1];
+                    if (row0 < p.numel)
+                        *reinterpret_cast<__half2*>(st + stash_block(rowBase, COUT, m * 2, j * 2 + h)) = pre[h][0];
+                    if (row0 + 8 < p.numel)
+                        *reinterpret_cast<__half2*>(st + stash_block(rowBase, COUT, m * 2 + 1, j * 2 + h)) = pre[h][1];
                 }
             }
 #pragma unroll
@@ -630,22 +641,34 @@ __device__ __forceinline__ void backward_layers(const LaunchArgs& p, const __hal
     // delta = Act'(pre) * adj, in place (kernels/layer.cuh:216-229), pre-activations read back in fragment layout
     const __half* pre = p.fwdTmp + n32 * SL::preOffset(L);
     __half* dl = p.adjTmp + n32 * SL::deltaOffset(L);
+    // All pre-activations of a row tile are requested before the first delta is stored: the stores go to memory the
+    // compiler cannot tell apart from the stash, so a load placed after one would wait for it to issue, and the loads
+    // would run one memory latency after the other.
 #pragma unroll
-    for (int m = 0; m < MT; ++m)
+    for (int m = 0; m < MT; ++m) {
+        uint32_t x[KT][4];
+#pragma unroll
+        for (int k = 0; k < KT; ++k)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const long long row = rowBase + m * 16 + r + (e & 1) * 8;
+                const long long at = stash_block(rowBase, COUT, m * 2 + (e & 1), k * 2 + (e >> 1)) + (r * 8 + q * 2);
+                x[k][e] = row < p.numel ? __ldg(reinterpret_cast<const unsigned int*>(pre + at)) : 0u;
+            }
 #pragma unroll
         for (int k = 0; k < KT; ++k)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const long long row = rowBase + m * 16 + r + (e & 1) * 8;
                 const int col = k * 16 + (e >> 1) * 8 + q * 2;
-                __half2 x = __float2half2_rn(0.f);
-                if (row < p.numel) x = *reinterpret_cast<const __half2*>(pre + row * COUT + col);
-                const __half2 d = act_adjoint2<Act>(x, u32_as_h2(adj[m][k][e]), col);
+                const long long at = stash_block(rowBase, COUT, m * 2 + (e & 1), k * 2 + (e >> 1)) + (r * 8 + q * 2);
+                const __half2 d = act_adjoint2<Act>(u32_as_h2(x[k][e]), u32_as_h2(adj[m][k][e]), col);
                 adj[m][k][e] = h2_as_u32(d);
                 if constexpr ((FLAGS & FLAG_GRAD_WEIGHTS) != 0) {
-                    if (row < p.numel) *reinterpret_cast<__half2*>(dl + row * COUT + col) = d;
+                    if (row < p.numel) *reinterpret_cast<__half2*>(dl + at) = d;
                 }
             }
+    }
 
     if constexpr (L > 0 || NEED_ENC) {
         // adjIn (points x CIN) = delta (points x COUT) * W (COUT x CIN): B fragments by transposing ldmatrix
@@ -850,15 +873,24 @@ __device__ __forceinline__ void wgrad_layer(const LaunchArgs& p, unsigned char* 
     auto load_slab = [&](long long slab, int buf) {
         const long long row0 = slab * WG_SLAB;
         constexpr int DCH = COUT / 8, ACH = CIN / 8;
+        // 16-byte pieces (one point, 8 channels). Deltas and pre-activations lie in 8 x 8 blocks (stash_block) and are
+        // copied as they are: in shared memory an 8 x 8 block is then one 128-byte line, which is exactly what one
+        // ldmatrix matrix reads (no bank conflicts, no padding). The encoded input (L == 0) is row-major with padded rows.
         for (int i = threadIdx.x; i < WG_SLAB * DCH; i += WG_WARPS * 32) {
-            const int rr = i / DCH, cc = i % DCH;
+            const int rr = (i / (32 * DCH)) * 32 + (i % 32);        // the point of piece i (storage order)
             const bool ok = row0 + rr < p.numel;
-            cp_async16(smem_u32(sDbase + buf * WG_SLAB * DS + rr * DS + cc * 8), gD + (ok ? row0 + rr : 0) * COUT + cc * 8, ok);
+            cp_async16(smem_u32(sDbase + buf * WG_SLAB * DS + i * 8), gD + (ok ? row0 * COUT + i * 8 : 0), ok);
         }
         for (int i = threadIdx.x; i < WG_SLAB * ACH; i += WG_WARPS * 32) {
-            const int rr = i / ACH, cc = i % ACH;
-            const bool ok = row0 + rr < p.numel;
-            cp_async16(smem_u32(sAbase + buf * WG_SLAB * BS + rr * BS + cc * 8), gA + (ok ? row0 + rr : 0) * CIN + cc * 8, ok);
+            if constexpr (L == 0) {
+                const int rr = i / ACH, cc = i % ACH;
+                const bool ok = row0 + rr < p.numel;
+                cp_async16(smem_u32(sAbase + buf * WG_SLAB * BS + rr * BS + cc * 8), gA + (ok ? row0 + rr : 0) * CIN + cc * 8, ok);
+            } else {
+                const int rr = (i / (32 * ACH)) * 32 + (i % 32);
+                const bool ok = row0 + rr < p.numel;
+                cp_async16(smem_u32(sAbase + buf * WG_SLAB * BS + i * 8), gA + (ok ? row0 * CIN + i * 8 : 0), ok);
+            }
         }
     };
 
@@ -880,8 +912,14 @@ __device__ __forceinline__ void wgrad_layer(const LaunchArgs& p, unsigned char* 
         const __half* a = sAbase + buf * WG_SLAB * BS;
         // B fragment (k = point, n = cin) of column block nb: transposing ldmatrix of the (point, cin) tile, then
         // a_{l-1} = Act_{l-1}(stashed pre-activation) on it
+        // offset of (point row, 8-channel column block cb) of a slab in the blocked layout
+        auto blocked = [](int row, int cb, int channels) {
+            return (row >> 5) * 32 * channels + ((cb * 4 + ((row & 31) >> 3)) * 64) + (row & 7) * 8;
+        };
         auto load_b = [&](int ks, int nb, uint32_t (&bf)[4]) {
-            ldmatrix_x4_trans(bf, smem_u32(a + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * BS + nb * 16 + (lane >> 4) * 8));
+            const int row = ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+            if constexpr (L == 0) ldmatrix_x4_trans(bf, smem_u32(a + row * BS + nb * 16 + (lane >> 4) * 8));
+            else ldmatrix_x4_trans(bf, smem_u32(a + blocked(row, nb * 2 + (lane >> 4), CIN)));
             if constexpr (L > 0) {
                 using ActPrev = typename Spec::template Act<(L > 0 ? L - 1 : 0)>;
 #pragma unroll
@@ -906,7 +944,7 @@ __device__ __forceinline__ void wgrad_layer(const LaunchArgs& p, unsigned char* 
                 const int mb = blk / NB, nb = blk % NB;
                 // A fragment = delta^T (m = cout, k = point): transposing ldmatrix of the (point, cout) tile
                 uint32_t af[4];
-                ldmatrix_x4_trans(af, smem_u32(d + (ks * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * DS + mb * 16 + ((lane >> 3) & 1) * 8));
+                ldmatrix_x4_trans(af, smem_u32(d + blocked(ks * 16 + (lane & 7) + ((lane >> 4) & 1) * 8, mb * 2 + ((lane >> 3) & 1), COUT)));
                 if constexpr (!SAME_NB) load_b(ks, nb, bf);
                 mma16816(acc[b][0], af, bf[0], bf[1]);
                 mma16816(acc[b][1], af, bf[2], bf[3]);

@@ -90,3 +90,26 @@ def pack_parameters(spec: "oracle.NetSpec", weights, biases):
 def load_golden(name):
     import os
     return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", name))
+
+
+def stash_rows(flat, n32, width):
+    """Row-major (N32, width) copy of one pre-activation or delta matrix of the stash. The kernels store such a matrix
+    as tiles of 32 points, each tile in blocks of 8 points x 8 channels, block (cb, rb) of a tile at (cb * 4 + rb) * 64
+    halfs and point-major inside (one mma fragment register of a warp = one 128-byte block). numpy array or torch tensor."""
+    blocks = flat.reshape(n32 // 32, width // 8, 4, 8, 8)            # tile, cb, rb, point, channel
+    if isinstance(blocks, np.ndarray):
+        return np.ascontiguousarray(blocks.transpose(0, 2, 3, 1, 4)).reshape(n32, width)
+    return blocks.permute(0, 2, 3, 1, 4).contiguous().reshape(n32, width)
+
+
+def stash_rows_all(flat, n32, widths):
+    """Row-major copies of consecutive stash matrices of the given widths, concatenated into one flat array again
+    (the layout the reference's kernels use for the same buffers)."""
+    out, off = [], 0
+    for w in widths:
+        out.append(stash_rows(flat[off:off + n32 * w], n32, w).reshape(-1))
+        off += n32 * w
+    if isinstance(out[0], np.ndarray):
+        return np.concatenate(out)
+    import torch
+    return torch.cat(out)

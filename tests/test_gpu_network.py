@@ -206,12 +206,15 @@ def test_inference_half_tables_and_strided_io():
 
 def _read_stash(spec, fwd_tmp, n):
     """Forward stash layout: [encoded input (N32, Cin0) | pre-activation of layer 0 (N32, Cout0) | layer 1 ...],
-    fp16, row-major, N32 = N rounded up to 32. Rows >= N are never written."""
+    fp16, N32 = N rounded up to 32; the encoded input row-major, the pre-activations in 8 x 8 blocks
+    (helpers.stash_rows). Rows >= N are never written."""
     n32 = (n + 31) // 32 * 32
     halfs = fwd_tmp.view(dtype=np.float16)
     out, off = [], 0
-    for width in [spec.layers[0].channels_in] + [l.channels_out for l in spec.layers]:
-        out.append(halfs[off:off + n32 * width].reshape(n32, width)[:n].astype(np.float32))
+    for i, width in enumerate([spec.layers[0].channels_in] + [l.channels_out for l in spec.layers]):
+        seg = halfs[off:off + n32 * width]
+        rows = seg.reshape(n32, width) if i == 0 else helpers.stash_rows(seg, n32, width)
+        out.append(rows[:n].astype(np.float32))
         off += n32 * width
     return out
 

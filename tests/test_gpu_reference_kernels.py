@@ -84,8 +84,9 @@ def _reference_backward(cfg):
 
 @pytest.mark.parametrize("name", ["config1", "config2", "config3_small"])
 def test_backward_matches_reference_kernel(name):
-    """The reference's NetworkKernelBackward, fed with the forward stash of THIS build (both use (N32, Cout) row-major
-    pre-activations per layer, src_cpp/src/fused_network.cpp:207-218), against this build's backward kernel: the delta
+    """The reference's NetworkKernelBackward, fed with the forward stash of THIS build (the reference uses (N32, Cout)
+    row-major pre-activations per layer, src_cpp/src/fused_network.cpp:207-218; this build's blocked matrices are
+    rearranged to that), against this build's backward kernel: the delta
     of every layer (what the weight gradients are computed from), the input gradient of identity encodings and the
     table gradient of the hash grid. Sharing the stash keeps activation derivatives identical on both sides; what
     remains is half (reference) against fp32 (here) accumulation in the delta chain."""
@@ -127,14 +128,16 @@ def test_backward_matches_reference_kernel(name):
 
     cin0 = spec.layers[0].channels_in
     stash_halfs = sum(l.channels_out for l in spec.layers)
-    pre = fwd[n32 * cin0: n32 * (cin0 + stash_halfs)]
+    widths = [l.channels_out for l in spec.layers]
+    # this build stores the matrices in 8 x 8 blocks; the reference's kernels read and write them row-major
+    pre = helpers.stash_rows_all(fwd[n32 * cin0: n32 * (cin0 + stash_halfs)], n32, widths)
     ref_grid_grads = [torch.zeros_like(t) if t is not None else None for t in tt]
     ref_adj_in, ref_deltas = ref(tx, tadj, tp, pre, tt, ref_grid_grads)
 
     off = 0
     for li, l in enumerate(spec.layers):
         c = l.channels_out
-        mine = bwd[n32 * off: n32 * (off + c)].view(n32, c)[:n].float().cpu().numpy()
+        mine = helpers.stash_rows(bwd[n32 * off: n32 * (off + c)], n32, c)[:n].float().cpu().numpy()
         theirs = ref_deltas[n32 * off: n32 * (off + c)].view(n32, c)[:n].float().cpu().numpy()
         if li == len(spec.layers) - 1:      # padded output channels carry no adjoint
             mine, theirs = mine[:, :spec.num_outputs], theirs[:, :spec.num_outputs]
@@ -160,7 +163,7 @@ def test_backward_matches_reference_kernel(name):
         ref_wu = ref_kernels.ReferenceWeightUpdate(cfg)
     except FileNotFoundError:
         pytest.skip("reference kernels were not built (no reference checkout at build time)")
-    deltas = bwd[: n32 * stash_halfs]
+    deltas = helpers.stash_rows_all(bwd[: n32 * stash_halfs], n32, widths)
     ref_grads = ref_wu(tx, pre, deltas, tt).cpu().numpy()
     mine = grads.cpu().numpy()
     for li, l in enumerate(spec.layers):
