@@ -224,8 +224,10 @@ struct PlaneLaunchers {
         if constexpr (groups == 0) {
             return cudaSuccess;
         } else {
+            // one CTA per 256 points: the hardware scheduler refills an SM as soon as a CTA retires, so the SMs drain
+            // together at the end (with fewer, looping CTAs some took one tile more than others)
             long long bx = (a.numel + 255) / 256;
-            const long long cap = static_cast<long long>(a.numSMs) * 8;
+            const long long cap = 1ll << 30;
             if (bx > cap) bx = cap;
             if (bx < 1) bx = 1;
             scatter_planes_kernel<Spec><<<static_cast<unsigned>(bx), 256, 0, s>>>(a);
