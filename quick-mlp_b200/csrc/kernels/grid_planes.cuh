@@ -195,17 +195,19 @@ __device__ __forceinline__ void scatter_group(const LaunchArgs& p, int g, const 
     }
 }
 
+constexpr int SCATTER_THREADS = 128;
+
 template <class Spec>
-__global__ void __launch_bounds__(256, 4) scatter_planes_kernel(const __grid_constant__ LaunchArgs p)
+__global__ void __launch_bounds__(SCATTER_THREADS, 1024 / SCATTER_THREADS) scatter_planes_kernel(const __grid_constant__ LaunchArgs p)
 {
     constexpr int groups = scatter_group_count<Spec>();
-    const long long tiles = (p.numel + 255) / 256;
-    // A CTA takes 256 points through all levels, starting at a level that depends on the CTA: at any moment the CTAs of
+    const long long tiles = (p.numel + SCATTER_THREADS - 1) / SCATTER_THREADS;
+    // A CTA takes its points through all levels, starting at a level that depends on the CTA: at any moment the CTAs of
     // the GPU are spread over all levels, so the reductions in flight go to many different rows and L2 slices (with all
     // CTAs on one small level, reductions to the same row queue up behind each other).
     const int first = static_cast<int>(blockIdx.x % groups);
     for (long long t = blockIdx.x; t < tiles; t += gridDim.x) {
-        const long long i = t * 256 + threadIdx.x;
+        const long long i = t * SCATTER_THREADS + threadIdx.x;
         if (i >= p.numel) continue;
         RowReader in{p.input + i * p.inS0, p.inS1};
         for (int gi = 0; gi < groups; ++gi) {
@@ -224,13 +226,13 @@ struct PlaneLaunchers {
         if constexpr (groups == 0) {
             return cudaSuccess;
         } else {
-            // one CTA per 256 points: the hardware scheduler refills an SM as soon as a CTA retires, so the SMs drain
+            // one CTA per SCATTER_THREADS points: the hardware scheduler refills an SM as soon as a CTA retires, so the SMs drain
             // together at the end (with fewer, looping CTAs some took one tile more than others)
-            long long bx = (a.numel + 255) / 256;
+            long long bx = (a.numel + SCATTER_THREADS - 1) / SCATTER_THREADS;
             const long long cap = 1ll << 30;
             if (bx > cap) bx = cap;
             if (bx < 1) bx = 1;
-            scatter_planes_kernel<Spec><<<static_cast<unsigned>(bx), 256, 0, s>>>(a);
+            scatter_planes_kernel<Spec><<<static_cast<unsigned>(bx), SCATTER_THREADS, 0, s>>>(a);
             return cudaGetLastError();
         }
     }
