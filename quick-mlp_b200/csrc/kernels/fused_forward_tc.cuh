@@ -329,7 +329,6 @@ __device__ __forceinline__ bool tc_stage(const LaunchArgs& p, TcSlot& sl, uint64
         if (ok) {
             tc_fence_after();
             constexpr int NCOL = LAST ? (Spec::NUM_OUTPUTS + 15) / 16 * 16 : COUT;   // accumulator columns that are needed
-#pragma unroll
             constexpr int LDW = TcLayout<Spec>::loadWidth();   // accumulator columns fetched per wait
             for (int c0 = 0; c0 < NCOL; c0 += LDW) {
                 float v[LDW];   // bias already added by the tensor core

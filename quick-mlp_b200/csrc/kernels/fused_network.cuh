@@ -843,22 +843,30 @@ __device__ __forceinline__ void wgrad_layer(const LaunchArgs& p, unsigned char* 
 {
     using SL = SmemLayout<Spec>;
     constexpr int CIN = Spec::CIN[L], COUT = Spec::COUT[L];
-    constexpr int DS = COUT + 8, BS = CIN + 8;          // smem row strides (halfs)
+    constexpr int BS = CIN + 8;                         // smem row stride of the row-major encoded input (halfs)
     constexpr int NBLK = (COUT / 16) * (CIN / 16);      // 16x16 output blocks
     constexpr int WB = NBLK >= 8 ? 8 : NBLK >= 4 ? 4 : NBLK >= 2 ? 2 : 1; // warps across blocks
     constexpr int KW = WG_WARPS / WB;                   // warps across the k16 steps of a slab
     constexpr int PB = (NBLK + WB - 1) / WB;            // blocks per warp
-    constexpr int KSTEPS = WG_SLAB / 16;
     constexpr bool BIAS = Spec::BOFF[L] >= 0;
 
+    // Points per pipeline stage of this layer: as many as the stage (sized for 64 points of the widest layer) holds, so
+    // that every layer moves about the same number of bytes per stage. With 64 points everywhere a 16 -> 16 layer
+    // spent its time on the two barriers per 4 KB slab (config 4: its CTAs finished last).
+    constexpr int A_STRIDE = L == 0 ? BS : CIN;         // the blocked operands need no padding
+    constexpr int SLAB_MAX = WgradSmem<Spec>::stageBytes() / ((COUT + A_STRIDE) * 2) / 64 * 64;
+    constexpr int SLAB = SLAB_MAX > 512 ? 512 : SLAB_MAX;
+    static_assert(SLAB >= WG_SLAB, "a stage holds at least 64 points of every layer");
+    constexpr int KSTEPS = SLAB / 16;
     constexpr int ST = WgradSmem<Spec>::stages();
-    __half* const sDbase = reinterpret_cast<__half*>(smem);            // [ST][WG_SLAB][DS]
-    __half* const sAbase = sDbase + ST * WG_SLAB * DS;                   // [ST][WG_SLAB][BS]
+    constexpr int STAGE_HALFS = SLAB * (COUT + A_STRIDE);
+    __half* const sDbase = reinterpret_cast<__half*>(smem);            // stage s: [SLAB x COUT | SLAB x A_STRIDE]
+    __half* const sAbase = sDbase + SLAB * COUT;
 
     const long long n32 = (p.numel + 31) / 32 * 32;
     const __half* gD = p.adjTmp + n32 * SL::deltaOffset(L);
     const __half* gA = L == 0 ? p.fwdTmp : p.fwdTmp + n32 * SL::preOffset(L > 0 ? L - 1 : 0);
-    const long long numSlabs = (p.numel + WG_SLAB - 1) / WG_SLAB;
+    const long long numSlabs = (p.numel + SLAB - 1) / SLAB;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wb = warp % WB, wk = warp / WB;
 
@@ -871,25 +879,25 @@ __device__ __forceinline__ void wgrad_layer(const LaunchArgs& p, unsigned char* 
     }
 
     auto load_slab = [&](long long slab, int buf) {
-        const long long row0 = slab * WG_SLAB;
+        const long long row0 = slab * SLAB;
         constexpr int DCH = COUT / 8, ACH = CIN / 8;
         // 16-byte pieces (one point, 8 channels). Deltas and pre-activations lie in 8 x 8 blocks (stash_block) and are
         // copied as they are: in shared memory an 8 x 8 block is then one 128-byte line, which is exactly what one
         // ldmatrix matrix reads (no bank conflicts, no padding). The encoded input (L == 0) is row-major with padded rows.
-        for (int i = threadIdx.x; i < WG_SLAB * DCH; i += WG_WARPS * 32) {
+        for (int i = threadIdx.x; i < SLAB * DCH; i += WG_WARPS * 32) {
             const int rr = (i / (32 * DCH)) * 32 + (i % 32);        // the point of piece i (storage order)
             const bool ok = row0 + rr < p.numel;
-            cp_async16(smem_u32(sDbase + buf * WG_SLAB * DS + i * 8), gD + (ok ? row0 * COUT + i * 8 : 0), ok);
+            cp_async16(smem_u32(sDbase + buf * STAGE_HALFS + i * 8), gD + (ok ? row0 * COUT + i * 8 : 0), ok);
         }
-        for (int i = threadIdx.x; i < WG_SLAB * ACH; i += WG_WARPS * 32) {
+        for (int i = threadIdx.x; i < SLAB * ACH; i += WG_WARPS * 32) {
             if constexpr (L == 0) {
                 const int rr = i / ACH, cc = i % ACH;
                 const bool ok = row0 + rr < p.numel;
-                cp_async16(smem_u32(sAbase + buf * WG_SLAB * BS + rr * BS + cc * 8), gA + (ok ? row0 + rr : 0) * CIN + cc * 8, ok);
+                cp_async16(smem_u32(sAbase + buf * STAGE_HALFS + rr * BS + cc * 8), gA + (ok ? row0 + rr : 0) * CIN + cc * 8, ok);
             } else {
                 const int rr = (i / (32 * ACH)) * 32 + (i % 32);
                 const bool ok = row0 + rr < p.numel;
-                cp_async16(smem_u32(sAbase + buf * WG_SLAB * BS + i * 8), gA + (ok ? row0 * CIN + i * 8 : 0), ok);
+                cp_async16(smem_u32(sAbase + buf * STAGE_HALFS + i * 8), gA + (ok ? row0 * CIN + i * 8 : 0), ok);
             }
         }
     };
@@ -908,8 +916,8 @@ __device__ __forceinline__ void wgrad_layer(const LaunchArgs& p, unsigned char* 
         cp_async_commit();
         cp_async_wait<ST - 1>();
         __syncthreads();
-        const __half* d = sDbase + buf * WG_SLAB * DS;
-        const __half* a = sAbase + buf * WG_SLAB * BS;
+        const __half* d = sDbase + buf * STAGE_HALFS;
+        const __half* a = sAbase + buf * STAGE_HALFS;
         // B fragment (k = point, n = cin) of column block nb: transposing ldmatrix of the (point, cin) tile, then
         // a_{l-1} = Act_{l-1}(stashed pre-activation) on it
         // offset of (point row, 8-channel column block cb) of a slab in the blocked layout
