@@ -365,14 +365,16 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
-        step(i)
-    barrier()
-    launches0 = net.launch_count()
+    # the clock sampler starts first (it needs a moment to come up), so that the warm-up steps run directly before
+    # the timed ones and the GPU does not idle in between
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
         time.sleep(0.15)
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    launches0 = net.launch_count()
     # A launch-bound workload (a few microseconds of kernel per step) is captured, K steps in a row, in one CUDA graph
     # and the timed region is one replay of it: otherwise the host's launch rate is what gets measured.
     graph = None
