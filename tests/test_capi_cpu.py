@@ -176,3 +176,21 @@ def test_line_integration_and_per_channel_host_side(tmp_path):
     with pytest.raises(QmlpError):
         bindings.QuickMLP.set_kernel_path(4)
     bindings.QuickMLP.set_kernel_path(0)
+
+
+def test_stash_block_layout_helper():
+    """helpers.stash_rows undoes the layout the kernels use for pre-activation and delta matrices: element (row, col) of
+    an (N32, C) matrix sits at tile * 32 * C + ((col // 8) * 4 + (row % 32) // 8) * 64 + (row % 8) * 8 + col % 8."""
+    import numpy as np
+    import helpers
+    n32, c = 96, 48
+    flat = np.zeros(n32 * c, dtype=np.float32)
+    for row in range(n32):
+        for col in range(c):
+            at = (row // 32) * 32 * c + ((col // 8) * 4 + (row % 32) // 8) * 64 + (row % 8) * 8 + col % 8
+            flat[at] = row * 1000 + col
+    rows = helpers.stash_rows(flat, n32, c)
+    want = np.arange(n32)[:, None] * 1000 + np.arange(c)[None, :]
+    assert np.array_equal(rows, want.astype(np.float32))
+    both = helpers.stash_rows_all(np.concatenate([flat, flat]), n32, [c, c])
+    assert np.array_equal(both.reshape(2, n32, c)[1], want.astype(np.float32))
