@@ -47,6 +47,12 @@ def lib():
         _lib.oracle_network_forward.argtypes = [C.POINTER(_Network), C.c_void_p, C.c_int64, C.c_void_p, C.c_int]
         _lib.oracle_network_forward.restype = None
         _lib.oracle_num_threads.restype = C.c_int
+        _lib.oracle_network_train_step.argtypes = [C.POINTER(_Network), C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                                                   C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                                   C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                                   C.POINTER(C.c_int64), C.c_int, C.c_float, C.c_float, C.c_float, C.c_float,
+                                                   C.c_int, C.c_int]
+        _lib.oracle_network_train_step.restype = C.c_double
     return _lib
 
 
@@ -98,3 +104,54 @@ class CpuNetwork:
         out = np.empty((x.shape[0], self.spec.num_outputs), dtype=np.float32)
         lib().oracle_network_forward(C.byref(self.net), x.ctypes.data, x.shape[0], out.ctypes.data, threads)
         return out
+
+    # -- training step (forward, L2 loss, backward, weight / bias / table gradients, Adam) ------------------------------
+    def _training_state(self):
+        if getattr(self, "_train", None) is None:
+            ne = len(self.spec.encodings)
+            z = lambda a: np.zeros_like(a)
+            st = {"gp": z(self._params), "mp": z(self._params), "vp": z(self._params),
+                  "gt": [z(t) if t is not None else None for t in self._tables],
+                  "mt": [z(t) if t is not None else None for t in self._tables],
+                  "vt": [z(t) if t is not None else None for t in self._tables], "step": 0}
+            ptrs = lambda arrs: (C.c_void_p * ne)(*[a.ctypes.data if a is not None else None for a in arrs])
+            st["gt_p"], st["mt_p"], st["vt_p"] = ptrs(st["gt"]), ptrs(st["mt"]), ptrs(st["vt"])
+            st["counts"] = (C.c_int64 * ne)(*[t.size if t is not None else 0 for t in self._tables])
+            self._train = st
+        return self._train
+
+    @property
+    def params(self) -> np.ndarray:
+        """The fp32 parameter vector the C side reads and (in train_step) updates in place."""
+        return self._params
+
+    @property
+    def tables(self):
+        return self._tables
+
+    def train_step(self, x: np.ndarray, target: np.ndarray, n_global: int = 0, lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-8,
+                   update=True, threads: int = 0) -> float:
+        """One host training step on (x, target); updates parameters, tables and Adam moments in place and returns the
+        sum of squared errors. With update=False the gradients are left in ``gradients()`` instead."""
+        st = self._training_state()
+        x = np.ascontiguousarray(x.astype(np.float32))
+        target = np.ascontiguousarray(target.astype(np.float32))
+        assert target.shape == (x.shape[0], self.spec.num_outputs)
+        if update:
+            st["step"] += 1
+        return float(lib().oracle_network_train_step(
+            C.byref(self.net), x.ctypes.data, target.ctypes.data, x.shape[0], n_global,
+            st["gp"].ctypes.data, st["mp"].ctypes.data, st["vp"].ctypes.data, self._params.size,
+            st["gt_p"], st["mt_p"], st["vt_p"], st["counts"], max(st["step"], 1), lr, beta1, beta2, eps, int(update), threads))
+
+    def gradients(self):
+        """(network gradient, [table gradient per encoding]) left by train_step(update=False)."""
+        st = self._training_state()
+        return st["gp"], st["gt"]
+
+    def zero_gradients(self):
+        st = self._training_state()
+        st["gp"][:] = 0
+        for g in st["gt"]:
+            if g is not None:
+                g[:] = 0

@@ -127,6 +127,49 @@ def test_cpp_restatement_matches_numpy_oracle(cfg):
     np.testing.assert_array_equal(b, c)
 
 
+@pytest.mark.parametrize("cfg", [specs.config2(), specs.config3(10), specs.config4(9, 8)])
+def test_cpp_training_step_matches_numpy_oracle(cfg):
+    """oracle_network_train_step (the CPU leg of the benchmark's training workloads): loss, weight / bias / table
+    gradients against network_backward, and two Adam steps against adam_step."""
+    import cpu_ref
+    spec = oracle.parse_spec(cfg)
+    params = helpers.xavier_parameters(spec, cfg, bias_scale=0.1).astype(np.float32)
+    tables = helpers.grid_tables(spec, scale=0.1)
+    x = helpers.uniform(3, 1, (777, spec.num_inputs), 0.0, 1.0)
+    target = helpers.uniform(3, 2, (777, spec.num_outputs), -1.0, 1.0)
+    net = cpu_ref.CpuNetwork(spec, params, tables)
+    loss = net.train_step(x, target, update=False)
+    out = oracle.network_forward(spec, params, x, tables)
+    g = oracle.network_backward(spec, params, x, oracle.mse_loss_grad(out, target), tables, want_input=False)
+    np.testing.assert_allclose(loss, float(((out - target) ** 2).sum()), rtol=1e-5)
+    gp, gt = net.gradients()
+    np.testing.assert_allclose(gp, g.grad_params, rtol=1e-3, atol=1e-6 * float(np.abs(g.grad_params).max()) + 1e-9)
+    for a, b in zip(gt, g.grad_encodings):
+        if b is not None:
+            np.testing.assert_allclose(a, b, rtol=1e-3, atol=1e-5 * float(np.abs(b).max()))
+    # two full steps: the moments carry over, the gradients are cleared in between
+    net.zero_gradients()
+    p, m, v = params.copy(), np.zeros_like(params), np.zeros_like(params)
+    tabs = [t.copy() if t is not None else None for t in tables]
+    tm = [np.zeros_like(t) if t is not None else None for t in tables]
+    tv = [np.zeros_like(t) if t is not None else None for t in tables]
+    for step in (1, 2):
+        net.train_step(x, target)
+        o = oracle.network_forward(spec, p, x, tabs)
+        gg = oracle.network_backward(spec, p, x, oracle.mse_loss_grad(o, target), tabs, want_input=False)
+        oracle.adam_step(p, gg.grad_params, m, v, step)
+        for i, t in enumerate(tabs):
+            if t is not None:
+                oracle.adam_step(t, gg.grad_encodings[i], tm[i], tv[i], step)
+    # Adam divides by sqrt(v): entries whose gradient is rounding noise move by about the learning rate in either
+    # direction, so the comparison allows a small fraction of them
+    helpers.assert_close(net.params - params, p - params, "network parameters after two steps", rtol=2e-2, atol=2e-4,
+                         max_violations=0.02)
+    for a, b, t0 in zip(net.tables, tabs, tables):
+        if b is not None:
+            helpers.assert_close(a - t0, b - t0, "table after two steps", rtol=2e-2, atol=2e-4, max_violations=0.02)
+
+
 def test_adam_matches_torch():
     import torch
     rng = np.random.default_rng(0)
