@@ -94,6 +94,13 @@ QMLP_API int qmlp_set_kernel_path(int path);
  * 1 = a kernel gave up on a bounded on-chip wait and its results are invalid. The reference has no counterpart (its
  * kernels contain no waits); debugging aids there are printf paths (src_cpp/include/qmlp/kernels/layer.cuh:28-41). */
 QMLP_API int qmlp_device_status(int* status);
+/* Per-kernel device timing: while enabled, every kernel the library launches is bracketed by a CUDA event pair on its
+ * stream; qmlp_read_kernel_timing waits for the recorded launches, sums them per kernel (ids: the library's kernel
+ * numbers, 100 = Adam, 101 = half-copy refresh) into the caller's arrays, forgets them and returns the number of
+ * distinct kernels. No counterpart in the reference (its only timing aid is the wall-clock script
+ * tests_py/qmlp_tests/profile_network.py:168-188). */
+QMLP_API int qmlp_set_kernel_timing(int enabled);
+QMLP_API int qmlp_read_kernel_timing(int max_entries, int* kernel_ids, float* milliseconds, int* launches);
 
 /* ---- FusedNetwork: src_cpp/include/qmlp/fused_network.h:16-340 ------------------------------- */
 /* FusedNetwork::FusedNetwork(cfg, parent), src_cpp/src/fused_network.cpp:33-223. cfg is the JSON text. */
@@ -149,6 +156,11 @@ QMLP_API int qmlp_network_forward(qmlp_network_t* net, const qmlp_tensor_t* inpu
 #define QMLP_STATIC_SCRATCH_BYTES (32u << 20)
 QMLP_API int qmlp_network_forward_static_scratch(qmlp_network_t* net, const qmlp_tensor_t* input, qmlp_tensor_t* output,
                                                  qmlp_stream_t stream);
+/* Device address and size of that fixed array on the current device, so that the stash the call above left there can
+ * be handed on: pass the address as tmp_forward of qmlp_network_adjoint for the same batch (nothing is allocated; the
+ * contents are those of the last qmlp_network_forward_static_scratch call on this device). No counterpart in the
+ * reference. */
+QMLP_API int qmlp_static_scratch(void** device_address, size_t* bytes);
 /* FusedNetwork::zeroGradients, src_cpp/src/fused_network.cpp:738-744 (asynchronous on `stream` here). */
 QMLP_API int qmlp_network_zero_gradients(qmlp_network_t* net, qmlp_stream_t stream);
 /* FusedNetwork::adjointMemory, src_cpp/src/fused_network.cpp:997-1010 */

@@ -100,13 +100,49 @@ void checkIO(Network& n, const qmlp_tensor_t* input, const qmlp_tensor_t* output
     checkDtype(output, QMLP_FLOAT, outName);
 }
 
+// Optional per-kernel device timing (qmlp_set_kernel_timing): an event pair around every launch the library makes,
+// read back and summed per kernel by qmlp_read_kernel_timing. Off by default: the events cost a little.
+struct KernelTimer {
+    struct Record { int id; cudaEvent_t begin, end; };
+    std::mutex mutex;
+    bool enabled = false;
+    std::vector<Record> records;
+} g_timer;
+
+constexpr int KERNEL_ID_ADAM = 100, KERNEL_ID_REFRESH_HALF = 101;
+
+struct TimedLaunch {
+    int id;
+    cudaStream_t stream;
+    cudaEvent_t begin = nullptr, end = nullptr;
+    TimedLaunch(int kernelId, cudaStream_t s) : id(kernelId), stream(s)
+    {
+        if (!g_timer.enabled) return;
+        if (cudaEventCreate(&begin) != cudaSuccess || cudaEventCreate(&end) != cudaSuccess) { begin = end = nullptr; return; }
+        cudaEventRecord(begin, stream);
+    }
+    ~TimedLaunch()
+    {
+        if (!begin) return;
+        cudaEventRecord(end, stream);
+        std::lock_guard<std::mutex> lock(g_timer.mutex);
+        g_timer.records.push_back({id, begin, end});
+    }
+};
+
+void launchModule(Network& n, KernelModule& m, int kernelId, const kernel::LaunchArgs& a, qmlp_stream_t stream)
+{
+    TimedLaunch timed(kernelId, static_cast<cudaStream_t>(stream));
+    int launches = 0;
+    checkLaunch(m.launch(kernelId, &a, static_cast<cudaStream_t>(stream), &launches), "kernel launch failed");
+    n.launchCount += launches;
+}
+
 void launchNet(Network& n, int kernelId, const kernel::LaunchArgs& a, qmlp_stream_t stream)
 {
     if (a.numel <= 0) return;
     auto m = n.module(n.currentHalfMask());
-    int launches = 0;
-    checkLaunch(m->launch(kernelId, &a, static_cast<cudaStream_t>(stream), &launches), "kernel launch failed");
-    n.launchCount += launches;
+    launchModule(n, *m, kernelId, a, stream);
 }
 
 // Backward launch. With `planes` (n32 x encoded channels halfs) and table gradients but no input gradients requested,
@@ -213,6 +249,40 @@ int qmlp_set_kernel_path(int path)
         throw std::runtime_error("kernel path must be 0 (best for spec and batch), 1 (mma.sync only), 2 (level-major grid pass) or 3 (tcgen05 at any batch size)");
     Library::instance().kernelPath = path;
     QMLP_CATCH
+}
+
+int qmlp_set_kernel_timing(int enabled)
+{
+    std::lock_guard<std::mutex> lock(g_timer.mutex);
+    g_timer.enabled = enabled != 0;
+    return QMLP_OK;
+}
+
+int qmlp_read_kernel_timing(int max_entries, int* kernel_ids, float* milliseconds, int* launches)
+{
+    std::vector<KernelTimer::Record> records;
+    {
+        std::lock_guard<std::mutex> lock(g_timer.mutex);
+        records.swap(g_timer.records);
+    }
+    int n = 0;
+    for (auto& r : records) {
+        float ms = 0.f;
+        const bool ok = cudaEventSynchronize(r.end) == cudaSuccess && cudaEventElapsedTime(&ms, r.begin, r.end) == cudaSuccess;
+        cudaEventDestroy(r.begin);
+        cudaEventDestroy(r.end);
+        if (!ok || !kernel_ids || !milliseconds || !launches) continue;
+        int at = 0;
+        while (at < n && kernel_ids[at] != r.id) ++at;
+        if (at == n) {
+            if (n >= max_entries) continue;
+            kernel_ids[n] = r.id; milliseconds[n] = 0.f; launches[n] = 0;
+            ++n;
+        }
+        milliseconds[at] += ms;
+        launches[at] += 1;
+    }
+    return n;
 }
 
 int qmlp_device_status(int* status)
@@ -364,12 +434,15 @@ static void inferenceLocked(Network& n, const qmlp_tensor_t* input, qmlp_tensor_
             a.planes = static_cast<__half*>(n.planes);
             a.planeStride = n.planeCapacity;
             int launches = 0;
-            const int e = m->launch(kernel::KERNEL_ENCODE_PLANES, &a, static_cast<cudaStream_t>(stream), &launches);
+            int e;
+            {
+                TimedLaunch timed(kernel::KERNEL_ENCODE_PLANES, static_cast<cudaStream_t>(stream));
+                e = m->launch(kernel::KERNEL_ENCODE_PLANES, &a, static_cast<cudaStream_t>(stream), &launches);
+            }
             if (e == static_cast<int>(cudaErrorNotSupported) && c0 == 0) { n.planesUnsupported = true; ok = false; break; }
             checkLaunch(e, "kernel launch failed");
             n.launchCount += launches;
-            checkLaunch(m->launch(kernel::KERNEL_INFERENCE_PLANES, &a, static_cast<cudaStream_t>(stream), &launches), "kernel launch failed");
-            n.launchCount += launches;
+            launchModule(n, *m, kernel::KERNEL_INFERENCE_PLANES, a, stream);
         }
         if (ok) return;
         a.numel = total;
@@ -868,8 +941,11 @@ int qmlp_trainer_refresh_half(qmlp_trainer_t* tr, qmlp_stream_t stream)
 {
     QMLP_TRY
     if (!tr->master) throw std::runtime_error("trainer buffers are not bound");
-    checkCuda(kernel::launchRefreshHalf(tr->master, tr->half, tr->fusedCount, Library::instance().smCount(),
-                                        static_cast<cudaStream_t>(stream)), "refresh_half");
+    {
+        TimedLaunch timed(KERNEL_ID_REFRESH_HALF, static_cast<cudaStream_t>(stream));
+        checkCuda(kernel::launchRefreshHalf(tr->master, tr->half, tr->fusedCount, Library::instance().smCount(),
+                                            static_cast<cudaStream_t>(stream)), "refresh_half");
+    }
     tr->net->launchCount += 1;
     QMLP_CATCH
 }
@@ -931,7 +1007,11 @@ int qmlp_trainer_gradients_part(qmlp_trainer_t* tr, const qmlp_tensor_t* input, 
             a.planeStride = n32;
             auto m = n.module(n.currentHalfMask());
             int launches = 0;
-            const int e = m->launch(kernel::KERNEL_ENCODE_PLANES, &a, static_cast<cudaStream_t>(stream), &launches);
+            int e;
+            {
+                TimedLaunch timed(kernel::KERNEL_ENCODE_PLANES, static_cast<cudaStream_t>(stream));
+                e = m->launch(kernel::KERNEL_ENCODE_PLANES, &a, static_cast<cudaStream_t>(stream), &launches);
+            }
             if (e == static_cast<int>(cudaErrorNotSupported)) {
                 n.planesUnsupported = true;
             } else {
@@ -959,10 +1039,13 @@ int qmlp_trainer_update(qmlp_trainer_t* tr, int64_t step, float grad_scale, qmlp
     if (step < 1) throw std::runtime_error("step is 1-based");
     const double bc1 = 1.0 - std::pow(static_cast<double>(tr->cfg.beta1), static_cast<double>(step));
     const double bc2 = 1.0 - std::pow(static_cast<double>(tr->cfg.beta2), static_cast<double>(step));
-    checkCuda(kernel::launchAdam(tr->master, tr->grad, tr->m, tr->v, tr->half, tr->fusedCount, grad_scale, tr->cfg.beta1,
-                                 tr->cfg.beta2, static_cast<float>(tr->cfg.learning_rate / bc1),
-                                 static_cast<float>(1.0 / std::sqrt(bc2)), tr->cfg.epsilon, Library::instance().smCount(),
-                                 static_cast<cudaStream_t>(stream)), "adam");
+    {
+        TimedLaunch timed(KERNEL_ID_ADAM, static_cast<cudaStream_t>(stream));
+        checkCuda(kernel::launchAdam(tr->master, tr->grad, tr->m, tr->v, tr->half, tr->fusedCount, grad_scale, tr->cfg.beta1,
+                                     tr->cfg.beta2, static_cast<float>(tr->cfg.learning_rate / bc1),
+                                     static_cast<float>(1.0 / std::sqrt(bc2)), tr->cfg.epsilon, Library::instance().smCount(),
+                                     static_cast<cudaStream_t>(stream)), "adam");
+    }
     tr->net->launchCount += 1;
     QMLP_CATCH
 }

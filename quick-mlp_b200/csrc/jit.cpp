@@ -4,6 +4,8 @@
 // src_cpp/src/fused_network.cpp:465-470 and src_cpp/src/iencoding.cpp:59-63) and its on-disk kernel cache.
 #include "host.hpp"
 
+#include <atomic>
+
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
@@ -83,33 +85,33 @@ std::string Library::resolveIncludeDir()
 
 int Library::smCount()
 {
-    static int cached[64] = {0};
+    static std::atomic<int> cached[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) throw cuda_error("cudaGetDevice failed: no CUDA device available");
-    if (dev < 0 || dev >= 64) dev = 0;
-    if (cached[dev] == 0) {
-        int n = 0;
+    if (dev < 0 || dev >= 64) throw cuda_error("device index out of range (at most 64 devices per process)");
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
         cudaError_t e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
         if (e != cudaSuccess) throw cuda_error(std::string("cudaDeviceGetAttribute: ") + cudaGetErrorString(e));
-        cached[dev] = n;
+        cached[dev].store(n, std::memory_order_relaxed);
     }
-    return cached[dev];
+    return n;
 }
 
 int* Library::statusWord()
 {
-    static int* words[64] = {nullptr};
+    static std::atomic<int*> words[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) throw cuda_error("cudaGetDevice failed: no CUDA device available");
-    if (dev < 0 || dev >= 64) dev = 0;
-    if (words[dev] == nullptr) {
+    if (dev < 0 || dev >= 64) throw cuda_error("device index out of range (at most 64 devices per process)");
+    int* w = words[dev].load(std::memory_order_acquire);
+    if (w == nullptr) {
         // the word is a __device__ variable of this library (zero at module load): nothing is allocated
-        int* w = nullptr;
         cudaError_t e = kernel::statusWordAddress(&w);
         if (e != cudaSuccess) throw cuda_error(std::string("status word lookup failed: ") + cudaGetErrorString(e));
-        words[dev] = w;
+        words[dev].store(w, std::memory_order_release);
     }
-    return words[dev];
+    return w;
 }
 
 static uint64_t fnv1a(const std::string& s, uint64_t h = 1469598103934665603ULL)
@@ -193,9 +195,12 @@ std::shared_ptr<KernelModule> getKernelModule(const std::string& kind, const std
     if (::stat(so.c_str(), &st) != 0) {
         // build it
         makeDirs(cache);
-        const std::string cu = cache + "/" + name + ".cu";
-        const std::string tmp = so + ".tmp" + std::to_string(::getpid());
-        const std::string log = cache + "/" + name + ".log";
+        // Several processes may meet the same missing instantiation at once (one rank per GPU on a cold cache): each
+        // builds from its own source, log and output file, and only the finished shared object is renamed into place.
+        const std::string unique = std::to_string(::getpid());
+        const std::string cu = cache + "/" + name + "." + unique + ".cu";
+        const std::string tmp = so + ".tmp" + unique;
+        const std::string log = cache + "/" + name + "." + unique + ".log";
         {
             std::ofstream out(cu);
             out << source;
@@ -223,6 +228,9 @@ std::shared_ptr<KernelModule> getKernelModule(const std::string& kind, const std
             ::unlink(tmp.c_str());
             throw compile_error("cannot move the built instantiation to '" + so + "'");
         }
+        // keep one copy of the generated source and of the compiler log beside the shared object
+        ::rename(cu.c_str(), (cache + "/" + name + ".cu").c_str());
+        ::rename(log.c_str(), (cache + "/" + name + ".log").c_str());
     }
     auto m = loadModule(name, so);
     reg[name] = m;

@@ -487,8 +487,8 @@ struct TcLaunchers {
         constexpr int threads = TL::warpgroups() * 128;
         static DeviceOnce once;   // function attributes are per device
         auto k = fused_forward_tc_kernel<Spec, PLANES>;
-        if (once.first()) {
-            cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        {
+            const cudaError_t e = once.run([&] { return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
             if (e != cudaSuccess) return e;
         }
         const long long tiles = (a.numel + TC_TILE - 1) / TC_TILE;

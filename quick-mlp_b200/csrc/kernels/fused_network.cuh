@@ -1014,15 +1014,22 @@ wgrad_kernel(const __grid_constant__ LaunchArgs p)
 
 // ---- host-side launchers (compiled into each instantiation) -------------------------------------------------------
 template <class Spec> struct TcLayout;     // fused_forward_tc.cuh
-// "first call on the current device" latch for per-device kernel attributes (a process may drive several GPUs)
+// Per-device latch for kernel attributes (a process may drive several GPUs): `run` performs `set` once per device and
+// marks the device only after `set` succeeded, so a failed call is tried again and no launch can pass a latch whose
+// attribute is not in place yet (a second thread that arrives early simply sets the same attribute again).
 struct DeviceOnce {
-    std::atomic<unsigned long long> seen{0};
-    bool first()
+    std::atomic<unsigned long long> done{0};
+    template <class F>
+    cudaError_t run(F set)
     {
         int d = 0;
-        cudaGetDevice(&d);
+        cudaError_t e = cudaGetDevice(&d);
+        if (e != cudaSuccess) return e;
         const unsigned long long bit = 1ull << (d & 63);
-        return (seen.fetch_or(bit) & bit) == 0;
+        if ((done.load(std::memory_order_acquire) & bit) != 0) return cudaSuccess;
+        e = set();
+        if (e == cudaSuccess) done.fetch_or(bit, std::memory_order_release);
+        return e;
     }
 };
 
@@ -1043,8 +1050,8 @@ struct NetworkLaunchers {
         constexpr int smem = SmemLayout<Spec>::totalBytes();
         static DeviceOnce once;   // function attributes are per device
         auto k = fused_forward_kernel<Spec, MODE>;
-        if (once.first()) {
-            cudaError_t e = setSmem(k, smem);
+        {
+            const cudaError_t e = once.run([&] { return setSmem(k, smem); });
             if (e != cudaSuccess) return e;
         }
         int perSM = 0;
@@ -1066,8 +1073,8 @@ struct NetworkLaunchers {
         constexpr int smem = SmemLayout<Spec>::totalBytes();
         static DeviceOnce once;   // function attributes are per device
         auto k = fused_backward_kernel<Spec, FLAGS>;
-        if (once.first()) {
-            cudaError_t e = setSmem(k, smem);
+        {
+            const cudaError_t e = once.run([&] { return setSmem(k, smem); });
             if (e != cudaSuccess) return e;
         }
         int perSM = 0;
@@ -1107,8 +1114,8 @@ struct NetworkLaunchers {
         constexpr int smem = WgradSmem<Spec>::bytes();
         static DeviceOnce once;   // function attributes are per device
         auto k = wgrad_kernel<Spec>;
-        if (once.first()) {
-            cudaError_t e = setSmem(k, smem);
+        {
+            const cudaError_t e = once.run([&] { return setSmem(k, smem); });
             if (e != cudaSuccess) return e;
         }
         // two CTAs per SM, fewer for small batches, never fewer than every layer needs to get one

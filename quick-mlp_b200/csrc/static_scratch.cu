@@ -16,6 +16,8 @@
 //     like any first call); make that first call before starting a stream capture.
 #include "host.hpp"
 
+#include <atomic>
+
 #include <cuda_runtime.h>
 
 namespace {
@@ -28,19 +30,19 @@ static __device__ __align__(256) unsigned char g_forwardScratch[QMLP_STATIC_SCRA
 // device, so it is looked up once per device with that device current.
 void* scratchAddressOnCurrentDevice()
 {
-    static void* address[64] = {nullptr};
+    static std::atomic<void*> address[64];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) throw qmlp::cuda_error(std::string("cudaGetDevice: ") + cudaGetErrorString(e));
     if (dev < 0 || dev >= 64) throw qmlp::cuda_error("device index out of range");
-    if (address[dev] == nullptr) {
-        void* ptr = nullptr;
+    void* ptr = address[dev].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
         e = cudaGetSymbolAddress(&ptr, g_forwardScratch);
         if (e != cudaSuccess || ptr == nullptr)
             throw qmlp::cuda_error(std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(e));
-        address[dev] = ptr;
+        address[dev].store(ptr, std::memory_order_release);
     }
-    return address[dev];
+    return ptr;
 }
 
 } // namespace
@@ -52,14 +54,14 @@ extern "C" int qmlp_network_forward_static_scratch(qmlp_network_t* net, const qm
         if (net == nullptr || input == nullptr || output == nullptr) throw std::runtime_error("null argument");
         if (input->ndim != 2) throw std::runtime_error("input has the wrong dimension, expected 2");
         const long long points = input->sizes[0];
-        const long long n32 = (points + 31) / 32 * 32;
-        const size_t need = static_cast<size_t>(n32) * net->impl->stashHalfsPerPoint() * 2;
-        if (need > static_cast<size_t>(QMLP_STATIC_SCRATCH_BYTES)) {
-            const long long maxPoints = static_cast<long long>(QMLP_STATIC_SCRATCH_BYTES) / (net->impl->stashHalfsPerPoint() * 2) / 32 * 32;
+        // the point count is compared before anything is multiplied, so that no product can wrap
+        const long long maxPoints = static_cast<long long>(QMLP_STATIC_SCRATCH_BYTES) / (net->impl->stashHalfsPerPoint() * 2) / 32 * 32;
+        if (points < 0) throw std::runtime_error("negative point count");
+        if (points > maxPoints) {
             throw std::runtime_error(qmlp::format(
-                "batch of %lld points needs %zu bytes of forward stash, more than the %zu bytes of static scratch "
+                "batch of %lld points needs more forward stash than the %zu bytes of static scratch "
                 "(at most %lld points for this network); use qmlp_network_forward with a caller-allocated buffer",
-                points, need, static_cast<size_t>(QMLP_STATIC_SCRATCH_BYTES), maxPoints));
+                points, static_cast<size_t>(QMLP_STATIC_SCRATCH_BYTES), maxPoints));
         }
         void* scratch = scratchAddressOnCurrentDevice();
         qmlp::forwardWithStashAt(*net->impl, input, output, scratch, stream);
@@ -70,6 +72,19 @@ extern "C" int qmlp_network_forward_static_scratch(qmlp_network_t* net, const qm
         return qmlp::reportError(QMLP_ERROR_CUDA, e.what());
     } catch (const qmlp::compile_error& e) {
         return qmlp::reportError(QMLP_ERROR_COMPILE, e.what());
+    } catch (const std::exception& e) {
+        return qmlp::reportError(QMLP_ERROR_RUNTIME, e.what());
+    }
+}
+
+extern "C" int qmlp_static_scratch(void** device_address, size_t* bytes)
+{
+    try {
+        if (device_address) *device_address = scratchAddressOnCurrentDevice();
+        if (bytes) *bytes = static_cast<size_t>(QMLP_STATIC_SCRATCH_BYTES);
+        return QMLP_OK;
+    } catch (const qmlp::cuda_error& e) {
+        return qmlp::reportError(QMLP_ERROR_CUDA, e.what());
     } catch (const std::exception& e) {
         return qmlp::reportError(QMLP_ERROR_RUNTIME, e.what());
     }

@@ -54,6 +54,8 @@ SIGNATURES = {
     "qmlp_set_kernel_include_dir": (C.c_int, [C.c_char_p]),
     "qmlp_set_kernel_path": (C.c_int, [C.c_int]),
     "qmlp_device_status": (C.c_int, [C.POINTER(C.c_int)]),
+    "qmlp_set_kernel_timing": (C.c_int, [C.c_int]),
+    "qmlp_read_kernel_timing": (C.c_int, [C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_float), C.POINTER(C.c_int)]),
     "qmlp_network_create": (C.c_int, [C.c_char_p, C.c_char_p, C.POINTER(_P)]),
     "qmlp_network_destroy": (None, [_P]),
     "qmlp_network_channels_in": (C.c_int, [_P]),
@@ -73,6 +75,7 @@ SIGNATURES = {
     "qmlp_network_forward_memory": (C.c_int, [_P, C.c_int64, C.c_int, C.POINTER(C.c_size_t)]),
     "qmlp_network_forward": (C.c_int, [_P, _TP, _TP, _P, _P]),
     "qmlp_network_forward_static_scratch": (C.c_int, [_P, _TP, _TP, _P]),
+    "qmlp_static_scratch": (C.c_int, [C.POINTER(_P), C.POINTER(C.c_size_t)]),
     "qmlp_network_zero_gradients": (C.c_int, [_P, _P]),
     "qmlp_network_adjoint_memory": (C.c_int, [_P, C.c_int64, C.c_int, C.POINTER(C.c_size_t)]),
     "qmlp_network_adjoint": (C.c_int, [_P, _TP, _TP, C.c_int, _TP, _P, _P, _P]),

@@ -82,13 +82,13 @@ WORKLOADS = {
                name="config1: identity 3->16 relu->1 relu, no bias, 65536 points, fused inference"),
     "c2": dict(points=1 << 22, mode="inference", flops=25088, bytes=16, lo=-1.0, hi=1.0,
                name="config2: identity 3->64 relu->64 celu->64 sine->64 relu->1, bias, 2^22 points, fused inference"),
-    "c3": dict(points=1 << 20, mode="train", flops=3 * 12416, bytes=3100, lo=0.0, hi=1.0,
+    "c3": dict(points=1 << 20, mode="train", flops=3 * 12416, bytes=3100, gather_bytes=512, lo=0.0, hi=1.0,
                name="config3: 3-D hash grid 16x2 (2^19) + 32->64->64->1, 2^20 points, fused training step"),
-    "c3i": dict(points=1 << 20, mode="inference", flops=12416, bytes=528, lo=0.0, hi=1.0, config="c3",
+    "c3i": dict(points=1 << 20, mode="inference", flops=12416, bytes=528, gather_bytes=512, lo=0.0, hi=1.0, config="c3",
                 name="config3: 3-D hash grid 16x2 (2^19) + 32->64->64->1, 2^20 points, fused inference"),
-    "c4": dict(points=1 << 21, mode="train", flops=3 * 27776, bytes=3600, lo=0.0, hi=1.0,
+    "c4": dict(points=1 << 21, mode="train", flops=3 * 27776, bytes=3600, gather_bytes=576, lo=0.0, hi=1.0,
                name="config4: dense 64^3x4 + hash 8x4 (2^18) + 36->128->64->16->4, 2^21 points per GPU, training step"),
-    "c5": dict(points=1 << 24, mode="inference", flops=82944, bytes=2080, lo=0.0, hi=1.0, sharded=True,
+    "c5": dict(points=1 << 24, mode="inference", flops=82944, bytes=2080, gather_bytes=2048, lo=0.0, hi=1.0, sharded=True,
                name="config5: 4-D hash grid 16x4 (2^22) + 64->128x3->4, 2^24 points sharded over the GPUs, fused inference"),
 }
 

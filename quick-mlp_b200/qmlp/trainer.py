@@ -107,7 +107,24 @@ class FusedTrainer:
         for i, p in enumerate(encoding_parameters):
             if p is not None and self.backend.segments[1 + i] >= 0:
                 self.segment(self.master, 1 + i).copy_(p.to(torch.float32))
+        self._sync_replicas()
         self.backend.refresh_half()
+
+    def _sync_replicas(self):
+        """Data-parallel replicas must start from the same parameters: rank 0's master copy (and Adam state) is broadcast,
+        so that a caller who seeds by rank, or loads a checkpoint on one rank only, still gets one consistent model."""
+        dist, world = self._world()
+        if world > 1:
+            src = dist.get_global_rank(self.process_group, 0) if self.process_group is not None else 0
+            for t in (self.master, self.adam_m, self.adam_v):
+                dist.broadcast(t, src=src, group=self.process_group)
+
+    def collectives_per_step(self, world_size: int) -> int:
+        """Number of all-reduce calls one step issues at this world size."""
+        if world_size <= 1:
+            return 0
+        table_starts = [s for s in self.backend.segments[1:] if s >= 0]
+        return 2 if (table_starts and getattr(self.backend, "split_gradients", False)) else 1
 
     def state_dict(self):
         return {"master": self.master, "adam_m": self.adam_m, "adam_v": self.adam_v, "step": self.step_count}
@@ -117,6 +134,7 @@ class FusedTrainer:
         self.adam_m.copy_(state["adam_m"])
         self.adam_v.copy_(state["adam_v"])
         self.step_count = int(state["step"])
+        self._sync_replicas()
         self.backend.refresh_half()
 
     # -- one step -----------------------------------------------------------------------------------------------------

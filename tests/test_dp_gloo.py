@@ -98,6 +98,8 @@ def _train(rank, world, x, t, steps):
     backend = OracleStep(cfg)
     tr = FusedTrainer(FakeNetwork(backend.spec), device="cpu", backend=backend)
     params = helpers.xavier_parameters(backend.spec, cfg, bias_scale=0.05).astype(np.float32)
+    if rank > 0:
+        params = params + np.float32(0.25)   # a replica seeded differently: set_parameters broadcasts rank 0's copy over it
     tr.set_parameters(torch.from_numpy(params), [torch.from_numpy(tb) if tb is not None else None
                                                  for tb in helpers.grid_tables(backend.spec, scale=0.1)])
     b, e = shard_points(x.shape[0], rank, world)
