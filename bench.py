@@ -611,6 +611,8 @@ def main():
     ap.add_argument("--fp32-tables", action="store_true", help="gather from fp32 grid tables (reference layout)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="only the primary workload")
+    ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
+                    help="tuning switch of the training step for an A/B measurement (qmlp_set_tuning), e.g. sort_points=0")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -639,6 +641,9 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     load_library()
     bindings.QuickMLP.set_log_level("error")
+    for item in args.tune:
+        k, _, v = item.partition("=")
+        bindings.QuickMLP.set_tuning(k, int(v))
 
     bench = Bench(args, rank, local_rank, world)
     key = args.workload
@@ -662,6 +667,8 @@ def main():
                 "e2e": r["e2e"], "host_link": r["host_link"], "gpu_launches": r["launches"], "clocks": r["clocks"],
                 "roofline": roofline_block(bench, r, args.fp32_tables), "kernels": r["kernels"],
                 "wall_s_timed_region": r["wall"], "host_binding": numa}
+        if args.tune:
+            line["tuning"] = args.tune
         if r["graph"]:
             line["launch"] = "the K steps are one CUDA graph (launch-bound workload); the timed region is one replay"
         if "dp_check" in r:

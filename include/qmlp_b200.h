@@ -94,6 +94,12 @@ QMLP_API int qmlp_set_kernel_path(int path);
  * 1 = a kernel gave up on a bounded on-chip wait and its results are invalid. The reference has no counterpart (its
  * kernels contain no waits); debugging aids there are printf paths (src_cpp/include/qmlp/kernels/layer.cuh:28-41). */
 QMLP_API int qmlp_device_status(int* status);
+/* Tuning switches of the fused training step, for measurements; -1 restores the library's own choice.
+ * "sort_points": copy a batch into spatial-bin order first (1; never chosen automatically: it loses on random batches); "split_scatter": table-gradient scatter as
+ * its own kernel (1) or inside the backward kernel (0); "scatter_runs": 0 sends every table-gradient contribution of
+ * the sorted scatter straight to the table instead of summing runs of points that share a cell first. Stand in for the reference's tuning options
+ * (src_cpp/src/fused_network.cpp:45-69). */
+QMLP_API int qmlp_set_tuning(const char* key, int value);
 /* Per-kernel device timing: while enabled, every kernel the library launches is bracketed by a CUDA event pair on its
  * stream; qmlp_read_kernel_timing waits for the recorded launches, sums them per kernel (ids: the library's kernel
  * numbers, 100 = Adam, 101 = half-copy refresh) into the caller's arrays, forgets them and returns the number of

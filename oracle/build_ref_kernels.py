@@ -396,8 +396,8 @@ def build(cfg, force=False, kind="inference"):
 
 def default_configs():
     """The configurations the GPU parity tests and the benchmark compare against the reference kernel."""
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import specs
+    sys.path.insert(0, os.path.join(ROOT, "quick-mlp_b200"))
+    from qmlp import configs as specs
     return {"config1": specs.config1(), "config2": specs.config2(),
             "config3_small": specs.config3(log2_hashmap_size=14), "config3": specs.config3(),
             "config4": specs.config4(), "config5_small": specs.config5(log2_hashmap_size=12), "config5": specs.config5()}

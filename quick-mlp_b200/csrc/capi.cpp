@@ -150,22 +150,30 @@ void launchNet(Network& n, int kernelId, const kernel::LaunchArgs& a, qmlp_strea
 // Both ways are bound by the L2 reduction rate (one 32-byte sector per clock and slice). The separate kernel merges
 // neighbouring rows of two fp32 features into one 16-byte reduction (a quarter fewer L2 operations; config 3: 951 ->
 // 848 us); with wider rows nothing can be merged and the fused scatter, which hides under the backward kernel's MMA
-// phases, is faster (config 4: 1627 us fused, 2058 us split). Hence: split only if every grid has two features.
-void launchBackward(Network& n, kernel::LaunchArgs& a, __half* planes, int64_t n32, qmlp_stream_t stream)
+// phases, is faster (config 4: 1627 us fused, 2058 us split). Hence: split only if every grid has two features, or if
+// the points are sorted into bins (`sorted`: a.input is the sorted copy and a.binStart its bin table), where the
+// separate kernel sums the coarse levels in shared memory whatever the row width.
+void launchBackward(Network& n, kernel::LaunchArgs& a, __half* planes, int64_t n32, qmlp_stream_t stream, bool sorted = false,
+                    bool scatterNow = true)
 {
-    bool gridGrad = false;
+    bool gridGrad = false, twoFeatures = true;
     for (int i = 0; i < a.numGrids; ++i) gridGrad = gridGrad || a.grids[i].grad != nullptr;
     for (int i = 0; i < n.numEncodings(); ++i)
-        if (auto* g = dynamic_cast<EncodingHashGrid*>(n.encoding(i).get())) gridGrad = gridGrad && g->features() == 2 && !g->isLine();
+        if (auto* g = dynamic_cast<EncodingHashGrid*>(n.encoding(i).get())) {
+            twoFeatures = twoFeatures && g->features() == 2;
+            gridGrad = gridGrad && !g->isLine();
+        }
+    const int want = Library::instance().splitScatter;
     const bool split = planes != nullptr && gridGrad && (a.flags & kernel::FLAG_GRAD_ENCODINGS) != 0 &&
-                       (a.flags & kernel::FLAG_GRAD_INPUT) == 0 && Library::instance().kernelPath != 1;
+                       (a.flags & kernel::FLAG_GRAD_INPUT) == 0 && Library::instance().kernelPath != 1 &&
+                       (want == 1 || (want != 0 && (twoFeatures || sorted)));
     if (split) {
         a.flags |= kernel::FLAG_SPLIT_SCATTER;
         a.planes = planes;
         a.planeStride = n32;
     }
     launchNet(n, kernel::KERNEL_BACKWARD, a, stream);
-    if (split) launchNet(n, kernel::KERNEL_SCATTER_PLANES, a, stream);
+    if (split && scatterNow) launchNet(n, sorted ? kernel::KERNEL_SCATTER_SORTED : kernel::KERNEL_SCATTER_PLANES, a, stream);
 }
 
 // layout of the adjoint scratch: [delta of every layer, if weight gradients | adjoint feature planes, if table
@@ -248,6 +256,18 @@ int qmlp_set_kernel_path(int path)
     if (path < 0 || path > 3)
         throw std::runtime_error("kernel path must be 0 (best for spec and batch), 1 (mma.sync only), 2 (level-major grid pass) or 3 (tcgen05 at any batch size)");
     Library::instance().kernelPath = path;
+    QMLP_CATCH
+}
+
+int qmlp_set_tuning(const char* key, int value)
+{
+    QMLP_TRY
+    const std::string k = key ? key : "";
+    Library& lib = Library::instance();
+    if (k == "sort_points") lib.sortPoints = value;
+    else if (k == "split_scatter") lib.splitScatter = value;
+    else if (k == "scatter_runs") lib.runAggregation = value;
+    else throw std::runtime_error("unknown tuning key '" + k + "' (sort_points, split_scatter, scatter_runs)");
     QMLP_CATCH
 }
 
@@ -851,6 +871,36 @@ int qmlp_activation_adjoint(qmlp_activation_t* act, const qmlp_tensor_t* input, 
 } // extern "C"
 
 // ---- fused training step -------------------------------------------------------------------------------------------
+// Workspace of one step, every part 256-byte aligned: forward stash and delta stash; dLoss/dOut; feature planes (forward
+// features first, then their adjoints); the copies of points and targets in bin order and the bin tables of the
+// spatially binned step (only for networks with a grid encoding).
+struct TrainerLayout {
+    size_t adjOut = 0, planes = 0, sortedInput = 0, sortedTarget = 0, bins = 0, total = 0;
+    int binCount = 0;
+};
+static TrainerLayout trainerLayout(const Network& n, int64_t n32)
+{
+    auto align = [](size_t b) { return (b + 255) / 256 * 256; };
+    TrainerLayout l;
+    size_t b = align(static_cast<size_t>(n32) * (n.stashHalfsPerPoint() + n.deltaHalfsPerPoint()) * 2);
+    l.adjOut = b;
+    b = align(b + static_cast<size_t>(n32) * n.channelsOut() * 4);
+    l.planes = b;
+    b = align(b + adjointPlaneBytes(n, n32, QMLP_GRADIENTS_NETWORK_WEIGHTS | QMLP_GRADIENTS_INPUT_ENCODINGS));
+    const int dims = n.sortDimensions();
+    if (dims > 0) {
+        l.binCount = kernel::sort_bin_count(dims);
+        l.sortedInput = b;
+        b = align(b + static_cast<size_t>(n32) * n.channelsIn() * 4);
+        l.sortedTarget = b;
+        b = align(b + static_cast<size_t>(n32) * n.channelsOut() * 4);
+        l.bins = b;
+        b = align(b + (static_cast<size_t>(l.binCount) * 3 + 1) * 4);
+    }
+    l.total = b;
+    return l;
+}
+
 struct qmlp_trainer {
     std::shared_ptr<Network> net;
     qmlp_trainer_config_t cfg;
@@ -896,13 +946,7 @@ int qmlp_trainer_workspace_bytes(qmlp_trainer_t* tr, int64_t num_elements, size_
 {
     QMLP_TRY
     const int64_t n32 = (num_elements + 31) / 32 * 32;
-    Network& n = *tr->net;
-    size_t b = static_cast<size_t>(n32) * (n.stashHalfsPerPoint() + n.deltaHalfsPerPoint()) * 2;
-    b = (b + 255) / 256 * 256;
-    b += static_cast<size_t>(n32) * n.channelsOut() * 4; // dLoss/dOut
-    b = (b + 255) / 256 * 256;
-    b += adjointPlaneBytes(n, n32, QMLP_GRADIENTS_NETWORK_WEIGHTS | QMLP_GRADIENTS_INPUT_ENCODINGS); // adjoint feature planes
-    *bytes = b;
+    *bytes = trainerLayout(*tr->net, n32).total;
     QMLP_CATCH
 }
 
@@ -972,14 +1016,13 @@ int qmlp_trainer_gradients_part(qmlp_trainer_t* tr, const qmlp_tensor_t* input, 
     if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0) throw std::runtime_error("workspace must be 256-byte aligned");
     if (global_points <= 0) global_points = numel;
     const int64_t n32 = (numel + 31) / 32 * 32;
+    const TrainerLayout lay = trainerLayout(n, n32);
     kernel::LaunchArgs a;
     fillCommon(n, a, input);
     unsigned char* ws = static_cast<unsigned char*>(workspace);
     a.fwdTmp = reinterpret_cast<__half*>(ws);
     a.adjTmp = a.fwdTmp + static_cast<size_t>(n32) * n.stashHalfsPerPoint();
-    size_t b = static_cast<size_t>(n32) * (n.stashHalfsPerPoint() + n.deltaHalfsPerPoint()) * 2;
-    b = (b + 255) / 256 * 256;
-    float* adjOut = reinterpret_cast<float*>(ws + b);
+    float* adjOut = reinterpret_cast<float*>(ws + lay.adjOut);
     // forward with stash; the output slot receives dLoss/dOut = 2 (out - target) / (global_points * C)
     a.output = adjOut;
     a.outS0 = n.channelsOut();
@@ -991,16 +1034,57 @@ int qmlp_trainer_gradients_part(qmlp_trainer_t* tr, const qmlp_tensor_t* input, 
     a.lossSum = loss_sum;
     bool anyGrid = false;
     for (int i = 0; i < n.numEncodings(); ++i) anyGrid = anyGrid || n.encoding(i)->hasParameters();
-    size_t pb = b + static_cast<size_t>(n32) * n.channelsOut() * 4;
-    pb = (pb + 255) / 256 * 256;
-    __half* planes = anyGrid ? reinterpret_cast<__half*>(ws + pb) : nullptr;
+    __half* planes = anyGrid ? reinterpret_cast<__half*>(ws + lay.planes) : nullptr;
+    // Gather-dominated batches (same rule as inference): the encodings are computed one grid level at a time into
+    // the plane region of the workspace, which is free until the backward kernel writes the adjoint planes there,
+    // and the forward kernel reads its layer-0 operand from the planes.
+    const Library& lib = Library::instance();
+    const int path = lib.kernelPath;
+    const bool wantPlanes = planes != nullptr && !n.planesUnsupported && a.numGrids > 0 && numel > 0 &&
+                            (path == 2 || (path == 0 && n.gathersPerPoint() >= 96 && numel >= (1 << 18)));
+    // Spatially sorted step (kernels/sorted_scatter.cuh), on request only (qmlp_set_tuning("sort_points", 1)): the points
+    // and targets are copied into bin order first and every kernel of the step works on the copies. Measured on the
+    // 3-D hash-grid benchmark network (2^20 uniformly random points): the gather gets quicker (289 -> 227 us) and the
+    // scatter sends a quarter fewer reductions, but reductions of neighbouring points arrive at the L2 together and
+    // queue up behind each other on the same sectors (scatter 538 -> 639 us), and the sort itself takes 70 to 140 us: a
+    // net loss for random batches, so it is not chosen automatically.
+    const bool wantSort = lay.binCount > 0 && !n.sortUnsupported && path != 1 && numel > 0 && lib.sortPoints == 1;
+    bool sorted = false;
+    if (wantSort) {
+        a.binCounts = reinterpret_cast<unsigned int*>(ws + lay.bins);
+        a.binStart = a.binCounts + lay.binCount;
+        a.binCursor = a.binStart + lay.binCount + 1;
+        a.sortedInput = reinterpret_cast<float*>(ws + lay.sortedInput);
+        a.sortedTarget = reinterpret_cast<float*>(ws + lay.sortedTarget);
+        a.runAggregation = lib.runAggregation;
+        if (parts & 1) {
+            auto m = n.module(n.currentHalfMask());
+            int launches = 0;
+            int e;
+            {
+                TimedLaunch timed(kernel::KERNEL_SORT_POINTS, static_cast<cudaStream_t>(stream));
+                e = m->launch(kernel::KERNEL_SORT_POINTS, &a, static_cast<cudaStream_t>(stream), &launches);
+            }
+            if (e == static_cast<int>(cudaErrorNotSupported)) {
+                n.sortUnsupported = true;
+            } else {
+                checkLaunch(e, "kernel launch failed");
+                n.launchCount += launches;
+                sorted = true;
+            }
+        } else {
+            sorted = true;   // the first part of this step sorted; the kernels of the second part read no points
+        }
+        if (sorted) {
+            a.input = a.sortedInput;
+            a.inS0 = n.channelsIn();
+            a.inS1 = 1;
+            a.target = a.sortedTarget;
+            a.tS0 = n.channelsOut();
+            a.tS1 = 1;
+        }
+    }
     if (parts & 1) {
-        // Gather-dominated batches (same rule as inference): the encodings are computed one grid level at a time into
-        // the plane region of the workspace, which is free until the backward kernel writes the adjoint planes there,
-        // and the forward kernel reads its layer-0 operand from the planes.
-        const int path = Library::instance().kernelPath;
-        const bool wantPlanes = planes != nullptr && !n.planesUnsupported && a.numGrids > 0 && numel > 0 &&
-                                (path == 2 || (path == 0 && n.gathersPerPoint() >= 96 && numel >= (1 << 18)));
         bool done = false;
         if (wantPlanes) {
             a.planes = planes;
@@ -1027,7 +1111,7 @@ int qmlp_trainer_gradients_part(qmlp_trainer_t* tr, const qmlp_tensor_t* input, 
     a.aoS0 = n.channelsOut();
     a.aoS1 = 1;
     a.flags = kernel::FLAG_GRAD_WEIGHTS | (anyGrid ? kernel::FLAG_GRAD_ENCODINGS : 0);
-    if (parts & 1) launchBackward(n, a, planes, n32, stream);
+    if (parts & 1) launchBackward(n, a, planes, n32, stream, sorted);
     if (parts & 2) launchNet(n, kernel::KERNEL_WGRAD, a, stream);
     QMLP_CATCH
 }

@@ -595,6 +595,14 @@ int Network::gathersPerPoint() const
     return g;
 }
 
+int Network::sortDimensions() const
+{
+    for (const auto& e : encodings_)
+        if (auto* h = dynamic_cast<const EncodingHashGrid*>(e.get()))
+            return h->isLine() ? 0 : h->dimension();   // a line integration samples many positions per point: no bins
+    return 0;
+}
+
 int64_t Network::gridTableBytes() const
 {
     int64_t b = 0;

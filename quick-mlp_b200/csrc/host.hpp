@@ -44,6 +44,10 @@ struct Library {
     std::string resolveIncludeDir();
     int smCount(); // of the current device
     int kernelPath = 0;    // 0: best kernels for the spec, 1: mma.sync kernels only
+    // tuning switches of the training step (qmlp_set_tuning): -1 = decided per network and batch
+    int sortPoints = -1;      // spatially sorted step (kernels/sorted_scatter.cuh): 1 on whenever instantiated, else off
+    int splitScatter = -1;    // table-gradient scatter as its own kernel: 0 inside the backward kernel, 1 separate
+    int runAggregation = 1;   // coarse levels of the sorted scatter: corner sums of a run of points in one cell kept in registers
     int* statusWord();     // device word of the current device that kernels set when a bounded wait gives up
 };
 
@@ -244,11 +248,13 @@ public:
     ~Network();
     int64_t gridTableBytes() const;   // bytes of all bound grid tables (what the gather walks through)
     int gathersPerPoint() const;      // table rows fetched per point by all plain grid encodings: sum of levels * 2^D
+    int sortDimensions() const;       // dimension of the grid whose bounding box bins the points of a training step (0: none)
     // level-major encoding pass (inference of networks with tables larger than L2): chunk buffer, allocated at the
     // first such call and kept until the network is destroyed
     void* planes = nullptr;
     int64_t planeCapacity = 0;        // points per chunk
     bool planesUnsupported = false;   // the spec has no instantiation of the plane kernels
+    bool sortUnsupported = false;     // the spec has no instantiation of the point sort
     HostPipeline hostPipeline;
     int ownedDevice = -1;             // device the library-owned buffers above live on (-1: none allocated yet)
     void claimDevice();               // first call: remember the current device; later calls: it must be the same

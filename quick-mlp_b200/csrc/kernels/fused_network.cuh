@@ -1035,6 +1035,7 @@ struct DeviceOnce {
 
 template <class Spec> struct TcLaunchers;
 template <class Spec> struct PlaneLaunchers;
+template <class Spec> struct SortLaunchers;
 
 template <class Spec>
 struct NetworkLaunchers {
@@ -1161,6 +1162,8 @@ struct NetworkLaunchers {
         case KERNEL_BACKWARD: e = backward(a, s); n = (a.flags & 7) ? 1 : 0; break;
         case KERNEL_WGRAD: e = wgrad(a, s); break;
         case KERNEL_SCATTER_PLANES: e = PlaneLaunchers<Spec>::scatter(a, s); break;
+        case KERNEL_SORT_POINTS: e = SortLaunchers<Spec>::sort(a, s, &n); break;
+        case KERNEL_SCATTER_SORTED: e = SortLaunchers<Spec>::scatter(a, s); break;
         default: break;
         }
         if (launches) *launches = (e == cudaSuccess) ? n : 0;

@@ -40,23 +40,32 @@ __device__ __forceinline__ void grid_cell(const float (&pos)[D], int resolution,
     }
 }
 
-// Element index (row*F + level offset) of corner `bits` (bit k set -> high corner in dimension k).
+// Element index (row*F + level offset) of the grid vertex with integer coordinates `v`.
 template <int D, int F>
-__device__ __forceinline__ unsigned int grid_corner_index(const GridCell<D>& c, const GridLevelP& lv, int bits)
+__device__ __forceinline__ unsigned int grid_vertex_index(const unsigned int (&v)[D], const GridLevelP& lv)
 {
     unsigned int idx;
     if (lv.hashed) {
-        idx = ((bits & 1) ? c.hi[0] : c.lo[0]) * hash_prime(0);
+        idx = v[0] * hash_prime(0);
 #pragma unroll
-        for (int k = 1; k < D; ++k) idx = ((((bits >> k) & 1) ? c.hi[k] : c.lo[k]) * hash_prime(k)) ^ idx;
+        for (int k = 1; k < D; ++k) idx = (v[k] * hash_prime(k)) ^ idx;
         idx = idx & (lv.hashGridSize - 1u); // == idx % hashGridSize: the table size is always 1 << log2_hashmap_size
     } else {
-        idx = (bits & 1) ? c.hi[0] : c.lo[0];
+        idx = v[0];
 #pragma unroll
-        for (int k = 1; k < D; ++k)
-            idx = (((bits >> k) & 1) ? c.hi[k] : c.lo[k]) + idx * static_cast<unsigned int>(lv.resolution);
+        for (int k = 1; k < D; ++k) idx = v[k] + idx * static_cast<unsigned int>(lv.resolution);
     }
     return idx * F + lv.offset;
+}
+
+// Element index of corner `bits` of a cell (bit k set -> high corner in dimension k).
+template <int D, int F>
+__device__ __forceinline__ unsigned int grid_corner_index(const GridCell<D>& c, const GridLevelP& lv, int bits)
+{
+    unsigned int v[D];
+#pragma unroll
+    for (int k = 0; k < D; ++k) v[k] = ((bits >> k) & 1) ? c.hi[k] : c.lo[k];
+    return grid_vertex_index<D, F>(v, lv);
 }
 
 // encoding_hashgrid.cuh:177-185,209-215: product taken from dimension D-1 down to 0

@@ -240,3 +240,5 @@ struct PlaneLaunchers {
 
 } // namespace kernel
 } // namespace qmlp
+
+#include "sorted_scatter.cuh"

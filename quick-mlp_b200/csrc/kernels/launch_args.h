@@ -63,8 +63,25 @@ struct LaunchArgs {
     int* status;                                   // device word set to 1 when a kernel gave up on a bounded wait
     __half* planes;                                // encoded features (or their adjoints) of a chunk of points, one plane per grid level
     long long planeStride;                         // points per plane (capacity of the chunk buffer)
+    // spatially binned training step (kernels/sorted_scatter.cuh): KERNEL_SORT_POINTS copies the points (and targets)
+    // into Morton-bin order; the kernels after it read the sorted copies through `input` / `target`
+    unsigned int* binCounts;                       // points per bin (sort_bin_count() entries), zeroed by the launcher
+    unsigned int* binStart;                        // first sorted point of every bin, sort_bin_count() + 1 entries
+    unsigned int* binCursor;                       // running insert position per bin
+    float* sortedInput;                            // (numel, NUM_INPUTS) row-major
+    float* sortedTarget;                           // (numel, NUM_OUTPUTS) row-major, may be null
+    int reservedSort;
+    int runAggregation;                            // 0: every point of every level scatters straight to the gradient table
     GridP grids[MAX_GRIDS];
 };
+
+// Bins of the point sort: a regular grid of 2^sort_bin_bits(D) cells per dimension over the bounding box of the first
+// grid encoding, numbered in Morton order (bit b of dimension d at bit b * D + d of the key).
+__host__ __device__ constexpr int sort_bin_bits(int dims)
+{
+    return dims <= 1 ? 16 : dims == 2 ? 9 : dims == 3 ? 6 : dims == 4 ? 4 : 3;
+}
+__host__ __device__ constexpr int sort_bin_count(int dims) { return 1 << (sort_bin_bits(dims) * dims); }
 
 // kernels a network instantiation exports through qmlp_spec_launch
 enum KernelId {
@@ -80,7 +97,9 @@ enum KernelId {
     KERNEL_ENCODE_PLANES = 9,      // encodings of a chunk of points -> level-major feature planes
     KERNEL_INFERENCE_PLANES = 10,  // layer chain reading the feature planes instead of running the encodings
     KERNEL_SCATTER_PLANES = 11,    // adjoint feature planes -> grid table gradients, one grid level at a time
-    KERNEL_FORWARD_LOSS_PLANES = 12 // KERNEL_FORWARD_LOSS with layer 0 fed from the planes of KERNEL_ENCODE_PLANES
+    KERNEL_FORWARD_LOSS_PLANES = 12, // KERNEL_FORWARD_LOSS with layer 0 fed from the planes of KERNEL_ENCODE_PLANES
+    KERNEL_SORT_POINTS = 13,         // points (and targets) -> Morton-bin order: count, scan, reorder
+    KERNEL_SCATTER_SORTED = 15       // KERNEL_SCATTER_PLANES for sorted points: coarse levels summed in shared memory first
 };
 
 // arguments of the stand-alone activation kernels
@@ -99,4 +118,4 @@ extern "C" {
 typedef int (*qmlp_spec_launch_fn)(int kernel, const void* args, cudaStream_t stream, int* launches);
 typedef int (*qmlp_spec_abi_fn)(void);
 }
-#define QMLP_SPEC_ABI_VERSION 5
+#define QMLP_SPEC_ABI_VERSION 7

@@ -34,10 +34,36 @@ def run_jobs(jobs):
     return errors
 
 
+def purge_stale(cache_dir=None):
+    """Instantiations are named by a hash of their source and of every template header, so a header change leaves the
+    old shared objects behind as dead weight. They are removed here whenever the headers differ from the ones the cache
+    was last filled with."""
+    import hashlib
+    cache_dir = cache_dir or os.path.join(HERE, "lib", "specs")
+    kernels = os.path.join(HERE, "csrc", "kernels")
+    h = hashlib.sha256()
+    for name in sorted(os.listdir(kernels)):
+        h.update(name.encode())
+        with open(os.path.join(kernels, name), "rb") as f:
+            h.update(f.read())
+    digest = h.hexdigest()
+    stamp = os.path.join(cache_dir, "headers.stamp")
+    if os.path.isdir(cache_dir):
+        old = open(stamp).read() if os.path.exists(stamp) else ""
+        if old != digest:
+            for name in os.listdir(cache_dir):
+                if name.startswith("qmlp_") and name.rsplit(".", 1)[-1] in ("so", "cu", "log"):
+                    os.unlink(os.path.join(cache_dir, name))
+    os.makedirs(cache_dir, exist_ok=True)
+    with open(stamp, "w") as f:
+        f.write(digest)
+
+
 def prebuild(jobs, processes=None):
     jobs = [list(j) for j in dict.fromkeys(tuple(j) for j in jobs)]
     if not jobs:
         return
+    purge_stale()
     processes = max(1, min(len(jobs), processes or os.cpu_count() or 4))
     with tempfile.TemporaryDirectory() as tmp:
         procs = []

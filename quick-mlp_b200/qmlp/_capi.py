@@ -54,6 +54,7 @@ SIGNATURES = {
     "qmlp_set_kernel_include_dir": (C.c_int, [C.c_char_p]),
     "qmlp_set_kernel_path": (C.c_int, [C.c_int]),
     "qmlp_device_status": (C.c_int, [C.POINTER(C.c_int)]),
+    "qmlp_set_tuning": (C.c_int, [C.c_char_p, C.c_int]),
     "qmlp_set_kernel_timing": (C.c_int, [C.c_int]),
     "qmlp_read_kernel_timing": (C.c_int, [C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_float), C.POINTER(C.c_int)]),
     "qmlp_network_create": (C.c_int, [C.c_char_p, C.c_char_p, C.POINTER(_P)]),

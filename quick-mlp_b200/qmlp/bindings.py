@@ -48,6 +48,11 @@ class QuickMLP:
         check(lib().qmlp_set_kernel_path(int(path)))
 
     @staticmethod
+    def set_tuning(key: str, value: int):
+        """Tuning switches of the fused training step ("sort_points", "split_scatter", "scatter_runs"); -1 = automatic."""
+        check(lib().qmlp_set_tuning(key.encode(), int(value)))
+
+    @staticmethod
     def device_status() -> int:
         """Synchronises and returns (then clears) the device status word: non-zero means a kernel gave up on a
         bounded wait and its outputs are invalid."""

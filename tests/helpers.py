@@ -71,7 +71,15 @@ def grid_tables(spec: "oracle.NetSpec", seed=13, scale=1.0):
     """One fp32 table per encoding (None for encodings without parameters), U(+-scale)."""
     out = []
     for i, e in enumerate(spec.encodings):
-        out.append(uniform(seed, 500 + i, (e.num_parameters,), -scale, scale) if e.num_parameters else None)
+        if not e.num_parameters:
+            out.append(None)
+        elif e.num_parameters > (1 << 22):
+            # full-size benchmark tables (up to 220 M entries): numpy's generator is an order of magnitude quicker than
+            # the portable counter-based one and nothing outside this process has to reproduce these values
+            rng = np.random.default_rng(seed * 1000 + i)
+            out.append(((rng.random(e.num_parameters, dtype=np.float32) * 2 - 1) * np.float32(scale)).astype(np.float32))
+        else:
+            out.append(uniform(seed, 500 + i, (e.num_parameters,), -scale, scale))
     return out
 
 

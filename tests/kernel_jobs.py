@@ -24,6 +24,12 @@ def jobs():
     for cfg in (tt.smooth_config3(), specs.config3(log2_hashmap_size=14)):
         out.append(("net", json.dumps(cfg), 0))
         out.append(("net", json.dumps(cfg), 1))
+    out.append(("net", json.dumps(tt.two_grid_config()), 3))
+    for d in (2, 4):
+        out.append(("net", json.dumps(tt.dims_config(d)), 0))
+    import test_gpu_full_size as tf
+    for cfg in tf.probe_encodings():
+        out.append(("enc", json.dumps(cfg), 0))
     for name, cfg in te.encoding_cases().items():
         out.append(("enc", json.dumps(cfg), 0))
     for cfg in (specs.hashgrid(3, 6, 1, 14, 8, 300), specs.hashgrid(4, 4, 1, 16, 8, 64), specs.hashgrid(2, 5, 1, -1, 4, 64)):

@@ -33,6 +33,10 @@ CASES = {
     "config2": (specs.config2, (-1.0, 1.0), 100_003),
     "config3_small": (lambda: specs.config3(log2_hashmap_size=14), (0.0, 1.0), 50_001),
     "config5_small": (lambda: specs.config5(log2_hashmap_size=12), (0.0, 1.0), 20_000),
+    # the benchmark networks at their full table sizes (2^19 rows per level; 64^3 dense + 2^18; 2^22 rows per level)
+    "config3": (specs.config3, (0.0, 1.0), 20_000),
+    "config4": (specs.config4, (0.0, 1.0), 20_000),
+    "config5": (specs.config5, (0.0, 1.0), 8_000),
 }
 
 
@@ -82,7 +86,7 @@ def _reference_backward(cfg):
         pytest.skip("reference kernels were not built (no reference checkout at build time)")
 
 
-@pytest.mark.parametrize("name", ["config1", "config2", "config3_small"])
+@pytest.mark.parametrize("name", ["config1", "config2", "config3_small", "config3", "config4"])
 def test_backward_matches_reference_kernel(name):
     """The reference's NetworkKernelBackward, fed with the forward stash of THIS build (the reference uses (N32, Cout)
     row-major pre-activations per layer, src_cpp/src/fused_network.cpp:207-218; this build's blocked matrices are

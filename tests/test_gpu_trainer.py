@@ -26,6 +26,20 @@ def smooth_config3(log2_hashmap_size=11):
     return cfg
 
 
+def two_grid_config():
+    """The mixed-encoding benchmark network (dense grid + hash grid, four features per row, 36 -> 128 -> 64 -> 16 -> 4) with
+    small tables and celu in place of relu (continuous derivative: entry-by-entry comparison of gradients)."""
+    cfg = specs.config4(log2_hashmap_size=12, dense_resolution=16)
+    for layer in cfg["network"]:
+        if layer["activation"] == "relu":
+            layer["activation"] = "celu"
+    return cfg
+
+
+def dims_config(dims):
+    return specs.grid_net(dims, [specs.hashgrid(dims, 6, 2, 11, 4, 96)], [32, 2], ["celu", "identity"])
+
+
 @pytest.fixture
 def kernel_path(request):
     """Library-wide kernel path for one test (2: level-major encoding pass for every grid network, which the automatic
@@ -36,9 +50,26 @@ def kernel_path(request):
     bindings.QuickMLP.set_kernel_path(0)
 
 
+@pytest.fixture
+def tuning(request):
+    """Library-wide tuning switches of the training step for one test, restored to automatic afterwards."""
+    from qmlp import bindings
+    for key, value in request.param.items():
+        bindings.QuickMLP.set_tuning(key, value)
+    yield request.param
+    for key in ("sort_points", "split_scatter"):
+        bindings.QuickMLP.set_tuning(key, -1)
+    bindings.QuickMLP.set_tuning("scatter_runs", 1)
+
+
+SORT_MODES = [{"sort_points": 0}, {"sort_points": 1}, {"sort_points": 1, "scatter_runs": 0}]
+SORT_IDS = ["unsorted", "sorted", "sorted_noruns"]
+
+
+@pytest.mark.parametrize("tuning", SORT_MODES, indirect=True, ids=SORT_IDS)
 @pytest.mark.parametrize("kernel_path", [0, 2], indirect=True)
 @pytest.mark.parametrize("half_tables", [True, False])
-def test_training_steps_match_oracle(half_tables, kernel_path):
+def test_training_steps_match_oracle(half_tables, kernel_path, tuning):
     import torch
     from qmlp import bindings
     from qmlp.trainer import FusedTrainer
@@ -75,6 +106,84 @@ def test_training_steps_match_oracle(half_tables, kernel_path):
     assert torch.equal(tr.half[: spec.num_parameters], tr.master[: spec.num_parameters].half())
     loss = tr.mean_loss(n * steps)
     assert np.isfinite(loss) and loss > 0
+
+
+def _step_gradients(cfg, x, t, half_tables, table_scale=0.1):
+    """Fused gradient vector of one step (before Adam) from the CUDA kernels, with the trainer and the oracle inputs."""
+    import torch
+    from qmlp import bindings
+    from qmlp.trainer import FusedTrainer
+    spec = oracle.parse_spec(cfg)
+    net = bindings.Network(json.dumps(cfg))
+    params = helpers.xavier_parameters(spec, cfg, bias_scale=0.05).astype(np.float32)
+    tables = helpers.grid_tables(spec, scale=table_scale)
+    tr = FusedTrainer(net, grid_half_copy=half_tables)
+    tr.set_parameters(torch.from_numpy(params).cuda(), [torch.from_numpy(tb).cuda() if tb is not None else None for tb in tables])
+    tr.backend.gradients(torch.from_numpy(x).cuda(), torch.from_numpy(t).cuda(), x.shape[0], tr.loss_sum)
+    torch.cuda.synchronize()
+    return tr, spec, params, tables
+
+
+def _targets4(x):
+    return np.stack([np.sin(8 * x[:, 0]) * np.cos(6 * x[:, 1]), np.cos(5 * x[:, 2]), np.sin(3 * x[:, 0] + 2 * x[:, 1]),
+                     np.cos(4 * x[:, 1]) * np.sin(7 * x[:, 2])], 1).astype(np.float32)
+
+
+@pytest.mark.parametrize("tuning", SORT_MODES + [{"sort_points": 1, "split_scatter": 0}], indirect=True,
+                         ids=SORT_IDS + ["sorted_inline_scatter"])
+@pytest.mark.parametrize("kernel_path", [0, 2], indirect=True)
+def test_step_gradients_two_grids_four_features(kernel_path, tuning):
+    """Dense grid + hash grid with four features per row on the same inputs (the shape of the mixed-encoding benchmark
+    network, small tables): weight, bias and both table gradients of one step against the oracle, on every path of the
+    step (points sorted into bins or not, runs of points in one cell summed in registers or not, scatter inside the backward
+    kernel or separate)."""
+    cfg = two_grid_config()
+    n = 6000
+    x = helpers.uniform(21, 1, (n, 3))
+    t = _targets4(x)
+    tr, spec, params, tables = _step_gradients(cfg, x, t, half_tables=True)
+    w16 = params.astype(np.float16)
+    t16 = [tb.astype(np.float16).astype(np.float32) for tb in tables]
+    out = oracle.network_forward(spec, w16, x, t16, half=True)
+    g = oracle.network_backward(spec, w16, x, oracle.mse_loss_grad(out, t), t16, half=True, want_input=False)
+    got_w = tr.segment(tr.gradient, 0).cpu().numpy()
+    scale = float(np.abs(g.grad_params).max())
+    helpers.assert_close(got_w, g.grad_params, "weight and bias gradients", rtol=5e-2, atol=2e-2 * scale, max_violations=0.02)
+    for i in range(2):
+        got = tr.segment(tr.gradient, 1 + i).cpu().numpy()
+        want = g.grad_encodings[i]
+        helpers.assert_close(got, want, f"table gradient of encoding {i}", rtol=5e-2, atol=2e-2 * float(np.abs(want).max()),
+                             max_violations=0.02)
+        # every contribution arrives exactly once: the totals agree far more closely than single rows
+        assert abs(float(got.sum()) - float(want.sum())) <= 2e-2 * float(np.abs(want).sum())
+
+
+@pytest.mark.parametrize("dims", [2, 4])
+def test_sorted_step_other_dimensions(dims):
+    """Bins of the point sort in two and four dimensions (512 x 512 and 16^4 bins): sorted and unsorted steps give the same
+    gradients, and both match the oracle."""
+    import torch
+    from qmlp import bindings
+    cfg = dims_config(dims)
+    n = 5000
+    x = helpers.uniform(31, dims, (n, dims), -0.05, 1.05)          # some points outside the bounding box: border bins
+    t = helpers.uniform(31, 9, (n, 2), -1.0, 1.0)
+    grads = []
+    try:
+        for sort in (0, 1):
+            bindings.QuickMLP.set_tuning("sort_points", sort)
+            tr, spec, params, tables = _step_gradients(cfg, x, t, half_tables=False)
+            grads.append(tr.gradient.cpu().numpy().copy())
+    finally:
+        bindings.QuickMLP.set_tuning("sort_points", -1)
+    scale = float(np.abs(grads[0]).max())
+    helpers.assert_close(grads[1], grads[0], "sorted against unsorted step", rtol=1e-2, atol=2e-3 * scale, max_violations=0.002)
+    w16 = params.astype(np.float16)
+    out = oracle.network_forward(spec, w16, x, tables, half=True)
+    g = oracle.network_backward(spec, w16, x, oracle.mse_loss_grad(out, t), tables, half=True, want_input=False)
+    want = g.grad_encodings[0]
+    got = grads[1][tr.backend.segments[1]:tr.backend.segments[1] + want.size]
+    helpers.assert_close(got, want, "table gradient", rtol=5e-2, atol=2e-2 * float(np.abs(want).max()), max_violations=0.02)
 
 
 def test_loss_decreases_on_config3_small():
