@@ -383,6 +383,8 @@ class Bench:
         trainer = None
         if w["mode"] == "train":
             trainer = FusedTrainer(net, lr=1e-2, grid_half_copy=not args.fp32_tables, device=dev)
+            if args.dp_levels_per_launch >= 0:
+                trainer.level_group_size = args.dp_levels_per_launch
             trainer.set_parameters(params.float(), [t.float() if t is not None else None for t in tables])
             targets = [targets_of(x, num_outputs, torch).contiguous() for x in xs]
 
@@ -611,6 +613,9 @@ def main():
     ap.add_argument("--fp32-tables", action="store_true", help="gather from fp32 grid tables (reference layout)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="only the primary workload")
+    ap.add_argument("--dp-levels-per-launch", type=int, default=-1,
+                    help="grid levels per scatter launch of the data-parallel step (0: one launch, one all-reduce of all "
+                         "table gradients under the weight-gradient kernel; default: the trainer's own choice)")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
                     help="tuning switch of the training step for an A/B measurement (qmlp_set_tuning), e.g. sort_points=0")
     args = ap.parse_args()

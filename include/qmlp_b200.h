@@ -266,10 +266,18 @@ QMLP_API int qmlp_trainer_gradients(qmlp_trainer_t* tr, const qmlp_tensor_t* inp
 /* The same step in two parts, so that a data-parallel caller can start the all-reduce of the (large) table-gradient
  * segments while the weight gradients are still being computed: parts = 1 runs forward, backward and the table-gradient
  * scatter (afterwards the encoding segments of the gradient buffer are final), parts = 2 the weight/bias gradients of
- * the layers (needs part 1 of the same batch in the same workspace), parts = 3 both. */
+ * the layers (needs part 1 of the same batch in the same workspace), parts = 3 both. Finer still, for networks whose
+ * table gradients are scattered by a kernel of their own (qmlp_trainer_scatter_levels > 0): parts = 4 runs forward and
+ * backward and leaves the adjoint feature planes in the workspace; parts = 8 | first << 8 | end << 16 then scatters
+ * the grid levels [first, end) (numbered over all grids as qmlp_trainer_scatter_levels lists them), after which their
+ * part of the gradient buffer is final; every level must be scattered exactly once before qmlp_trainer_update. */
 QMLP_API int qmlp_trainer_gradients_part(qmlp_trainer_t* tr, const qmlp_tensor_t* input, const qmlp_tensor_t* target,
                                          int64_t global_points, void* workspace, size_t workspace_bytes,
                                          float* loss_sum, int parts, qmlp_stream_t stream);
+/* Grid levels in scatter order with their element ranges [fused_begin, fused_end) in the fused buffers (arrays of
+ * max_levels entries, may be NULL). Returns the number of levels, or 0 when this network's table gradients are not
+ * scattered by a kernel of their own (then only parts 1, 2, 3 apply). */
+QMLP_API int qmlp_trainer_scatter_levels(qmlp_trainer_t* tr, int max_levels, int64_t* fused_begin, int64_t* fused_end);
 /* Adam over the fused buffer (gradient scaled by grad_scale first, e.g. 1 for a summed all-reduce of gradients
  * already normalised by global_points), refresh of the half copy, gradient buffer zeroed. step is 1-based. */
 QMLP_API int qmlp_trainer_update(qmlp_trainer_t* tr, int64_t step, float grad_scale, qmlp_stream_t stream);

@@ -153,8 +153,7 @@ void launchNet(Network& n, int kernelId, const kernel::LaunchArgs& a, qmlp_strea
 // phases, is faster (config 4: 1627 us fused, 2058 us split). Hence: split only if every grid has two features, or if
 // the points are sorted into bins (`sorted`: a.input is the sorted copy and a.binStart its bin table), where the
 // separate kernel sums the coarse levels in shared memory whatever the row width.
-void launchBackward(Network& n, kernel::LaunchArgs& a, __half* planes, int64_t n32, qmlp_stream_t stream, bool sorted = false,
-                    bool scatterNow = true)
+bool splitScatterChosen(Network& n, const kernel::LaunchArgs& a, bool havePlanes, bool sorted)
 {
     bool gridGrad = false, twoFeatures = true;
     for (int i = 0; i < a.numGrids; ++i) gridGrad = gridGrad || a.grids[i].grad != nullptr;
@@ -164,9 +163,14 @@ void launchBackward(Network& n, kernel::LaunchArgs& a, __half* planes, int64_t n
             gridGrad = gridGrad && !g->isLine();
         }
     const int want = Library::instance().splitScatter;
-    const bool split = planes != nullptr && gridGrad && (a.flags & kernel::FLAG_GRAD_ENCODINGS) != 0 &&
-                       (a.flags & kernel::FLAG_GRAD_INPUT) == 0 && Library::instance().kernelPath != 1 &&
-                       (want == 1 || (want != 0 && (twoFeatures || sorted)));
+    return havePlanes && gridGrad && (a.flags & kernel::FLAG_GRAD_ENCODINGS) != 0 && (a.flags & kernel::FLAG_GRAD_INPUT) == 0 &&
+           Library::instance().kernelPath != 1 && (want == 1 || (want != 0 && (twoFeatures || sorted)));
+}
+
+void launchBackward(Network& n, kernel::LaunchArgs& a, __half* planes, int64_t n32, qmlp_stream_t stream, bool sorted = false,
+                    bool scatterNow = true)
+{
+    const bool split = splitScatterChosen(n, a, planes != nullptr, sorted);
     if (split) {
         a.flags |= kernel::FLAG_SPLIT_SCATTER;
         a.planes = planes;
@@ -1004,7 +1008,11 @@ int qmlp_trainer_gradients_part(qmlp_trainer_t* tr, const qmlp_tensor_t* input, 
                                 void* workspace, size_t workspace_bytes, float* loss_sum, int parts, qmlp_stream_t stream)
 {
     QMLP_TRY
-    if (parts < 1 || parts > 3) throw std::runtime_error("parts must be 1 (up to the table gradients), 2 (weight gradients) or 3 (both)");
+    const int what = parts & 0xff;
+    const int levelBegin = (parts >> 8) & 0xff, levelEnd = (parts >> 16) & 0xff;
+    if (!(what == 1 || what == 2 || what == 3 || what == 4 || what == 8))
+        throw std::runtime_error("parts must be 1 (up to the table gradients), 2 (weight gradients), 3 (both), 4 (up to the adjoint "
+                                 "feature planes, scatter deferred) or 8 | first << 8 | end << 16 (scatter of a range of grid levels)");
     if (!tr->master) throw std::runtime_error("trainer buffers are not bound");
     Network& n = *tr->net;
     std::lock_guard<std::mutex> lock(n.mutex);
@@ -1057,7 +1065,7 @@ int qmlp_trainer_gradients_part(qmlp_trainer_t* tr, const qmlp_tensor_t* input, 
         a.sortedInput = reinterpret_cast<float*>(ws + lay.sortedInput);
         a.sortedTarget = reinterpret_cast<float*>(ws + lay.sortedTarget);
         a.runAggregation = lib.runAggregation;
-        if (parts & 1) {
+        if (what & 5) {
             auto m = n.module(n.currentHalfMask());
             int launches = 0;
             int e;
@@ -1084,7 +1092,7 @@ int qmlp_trainer_gradients_part(qmlp_trainer_t* tr, const qmlp_tensor_t* input, 
             a.tS1 = 1;
         }
     }
-    if (parts & 1) {
+    if (what & 5) {
         bool done = false;
         if (wantPlanes) {
             a.planes = planes;
@@ -1111,9 +1119,56 @@ int qmlp_trainer_gradients_part(qmlp_trainer_t* tr, const qmlp_tensor_t* input, 
     a.aoS0 = n.channelsOut();
     a.aoS1 = 1;
     a.flags = kernel::FLAG_GRAD_WEIGHTS | (anyGrid ? kernel::FLAG_GRAD_ENCODINGS : 0);
-    if (parts & 1) launchBackward(n, a, planes, n32, stream, sorted);
-    if (parts & 2) launchNet(n, kernel::KERNEL_WGRAD, a, stream);
+    if (what == 1 || what == 3) launchBackward(n, a, planes, n32, stream, sorted);
+    if (what == 4) {
+        if (sorted || !splitScatterChosen(n, a, planes != nullptr, sorted))
+            throw std::runtime_error("the scatter of this network is not a kernel of its own (qmlp_trainer_scatter_levels returns 0): use parts = 1");
+        launchBackward(n, a, planes, n32, stream, sorted, /*scatterNow=*/false);
+    }
+    if (what == 8) {
+        if (sorted || !splitScatterChosen(n, a, planes != nullptr, sorted))
+            throw std::runtime_error("the scatter of this network is not a kernel of its own (qmlp_trainer_scatter_levels returns 0)");
+        if (levelEnd <= levelBegin) throw std::runtime_error("empty range of grid levels");
+        a.flags |= kernel::FLAG_SPLIT_SCATTER;
+        a.planes = planes;
+        a.planeStride = n32;
+        a.scatterLevelBegin = levelBegin;
+        a.scatterLevelEnd = levelEnd;
+        launchNet(n, kernel::KERNEL_SCATTER_PLANES, a, stream);
+    }
+    if (what & 2) launchNet(n, kernel::KERNEL_WGRAD, a, stream);
     QMLP_CATCH
+}
+
+int qmlp_trainer_scatter_levels(qmlp_trainer_t* tr, int max_levels, int64_t* fused_begin, int64_t* fused_end)
+{
+    // levels of all plain grids in scatter order with their element ranges in the fused vectors; 0 when the table
+    // gradients are not scattered by a kernel of their own (rows wider than two features, a line integration, the
+    // mma.sync-only kernel path, the sorted step)
+    Network& n = *tr->net;
+    const Library& lib = Library::instance();
+    if (lib.kernelPath == 1 || lib.sortPoints == 1 || lib.splitScatter == 0) return 0;
+    bool two = true, any = false;
+    for (int i = 0; i < n.numEncodings(); ++i)
+        if (auto* g = dynamic_cast<EncodingHashGrid*>(n.encoding(i).get())) {
+            if (g->isLine()) return 0;
+            two = two && g->features() == 2;
+            any = true;
+        }
+    if (!any || (!two && lib.splitScatter != 1)) return 0;
+    int count = 0;
+    for (int i = 0; i < n.numEncodings(); ++i) {
+        auto* g = dynamic_cast<EncodingHashGrid*>(n.encoding(i).get());
+        if (!g) continue;
+        const auto& t = g->levelTable();
+        const int64_t seg = tr->segStart[1 + i];
+        for (size_t l = 0; l < t.size(); ++l, ++count) {
+            if (count >= max_levels) continue;
+            if (fused_begin) fused_begin[count] = seg + t[l].memoryOffset;
+            if (fused_end) fused_end[count] = seg + (l + 1 < t.size() ? t[l + 1].memoryOffset : g->parameterCount());
+        }
+    }
+    return count;
 }
 
 int qmlp_trainer_update(qmlp_trainer_t* tr, int64_t step, float grad_scale, qmlp_stream_t stream)

@@ -202,18 +202,23 @@ __global__ void __launch_bounds__(SCATTER_THREADS, 1024 / SCATTER_THREADS) scatt
 {
     constexpr int groups = scatter_group_count<Spec>();
     const long long tiles = (p.numel + SCATTER_THREADS - 1) / SCATTER_THREADS;
+    // levels of this launch (a data-parallel step scatters the levels in a few launches, so that the all-reduce of the
+    // levels that are finished runs under the scatter of the next ones)
+    const int begin = p.scatterLevelEnd > 0 ? p.scatterLevelBegin : 0;
+    const int count = (p.scatterLevelEnd > 0 ? (p.scatterLevelEnd < groups ? p.scatterLevelEnd : groups) : groups) - begin;
+    if (count <= 0) return;
     // A CTA takes its points through all levels, starting at a level that depends on the CTA: at any moment the CTAs of
     // the GPU are spread over all levels, so the reductions in flight go to many different rows and L2 slices (with all
     // CTAs on one small level, reductions to the same row queue up behind each other).
-    const int first = static_cast<int>(blockIdx.x % groups);
+    const int first = static_cast<int>(blockIdx.x % count);
     for (long long t = blockIdx.x; t < tiles; t += gridDim.x) {
         const long long i = t * SCATTER_THREADS + threadIdx.x;
         if (i >= p.numel) continue;
         RowReader in{p.input + i * p.inS0, p.inS1};
-        for (int gi = 0; gi < groups; ++gi) {
+        for (int gi = 0; gi < count; ++gi) {
             int g = first + gi;
-            if (g >= groups) g -= groups;
-            scatter_group<Spec, 0>(p, g, in, i);
+            if (g >= count) g -= count;
+            scatter_group<Spec, 0>(p, begin + g, in, i);
         }
     }
 }

@@ -70,7 +70,7 @@ struct LaunchArgs {
     unsigned int* binCursor;                       // running insert position per bin
     float* sortedInput;                            // (numel, NUM_INPUTS) row-major
     float* sortedTarget;                           // (numel, NUM_OUTPUTS) row-major, may be null
-    int reservedSort;
+    int scatterLevelBegin, scatterLevelEnd;        // KERNEL_SCATTER_PLANES: grid levels (counted over all grids) to scatter; 0, 0 = all
     int runAggregation;                            // 0: every point of every level scatters straight to the gradient table
     GridP grids[MAX_GRIDS];
 };
@@ -118,4 +118,4 @@ extern "C" {
 typedef int (*qmlp_spec_launch_fn)(int kernel, const void* args, cudaStream_t stream, int* launches);
 typedef int (*qmlp_spec_abi_fn)(void);
 }
-#define QMLP_SPEC_ABI_VERSION 7
+#define QMLP_SPEC_ABI_VERSION 8

@@ -115,6 +115,7 @@ SIGNATURES = {
     "qmlp_trainer_refresh_half": (C.c_int, [_P, _P]),
     "qmlp_trainer_gradients": (C.c_int, [_P, _TP, _TP, C.c_int64, _P, C.c_size_t, _P, _P]),
     "qmlp_trainer_gradients_part": (C.c_int, [_P, _TP, _TP, C.c_int64, _P, C.c_size_t, _P, C.c_int, _P]),
+    "qmlp_trainer_scatter_levels": (C.c_int, [_P, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
     "qmlp_trainer_update": (C.c_int, [_P, C.c_int64, C.c_float, _P]),
 }
 

@@ -54,8 +54,20 @@ class _CudaStep:
 
     split_gradients = True   # gradients(..., parts=1) then gradients(..., parts=2) is supported
 
+    def scatter_levels(self):
+        """[(first element, end element)] of every grid level in the fused buffers, in scatter order; [] when the table
+        gradients of this network are not scattered by a kernel of their own."""
+        n = lib().qmlp_trainer_scatter_levels(self._h, 0, None, None)
+        if n <= 0:
+            return []
+        b, e = (C.c_int64 * n)(), (C.c_int64 * n)()
+        lib().qmlp_trainer_scatter_levels(self._h, n, b, e)
+        return [(b[i], e[i]) for i in range(n)]
+
     def gradients(self, x, target, global_points, loss_sum, parts=3):
-        """parts: 1 = forward, backward, table gradients; 2 = weight/bias gradients of the layers; 3 = both."""
+        """parts: 1 = forward, backward, table gradients; 2 = weight/bias gradients of the layers; 3 = both;
+        4 = forward and backward with the scatter deferred; 8 | first << 8 | end << 16 = scatter of grid levels
+        [first, end)."""
         b = C.c_size_t()
         check(lib().qmlp_trainer_workspace_bytes(self._h, x.shape[0], C.byref(b)))
         if self._workspace is None or self._workspace.numel() < b.value:
@@ -91,6 +103,7 @@ class FusedTrainer:
         self.backend.bind(self.master, self.gradient, self.adam_m, self.adam_v, self.half)
         self.step_count = 0
         self.process_group = process_group
+        self.level_group_size = 3      # grid levels per scatter launch of a data-parallel step (0: one launch)
 
     # -- parameter access ---------------------------------------------------------------------------------------------
     def segment(self, buffer: torch.Tensor, index: int) -> Optional[torch.Tensor]:
@@ -119,11 +132,38 @@ class FusedTrainer:
             for t in (self.master, self.adam_m, self.adam_v):
                 dist.broadcast(t, src=src, group=self.process_group)
 
+    def _level_groups(self, world_size: int):
+        """[(first level, end level, first element, end element)]: the launches the table-gradient scatter is cut into
+        for a data-parallel step, each followed by the all-reduce of its part of the gradient vector. The element ranges
+        tile [first table segment, fused_count). Three levels per launch, the first launch takes what is left over (the
+        coarse levels are small): the last all-reduce is then short enough to hide under the weight-gradient kernel.
+        [] when the scatter is not a kernel of its own, or on one rank."""
+        key = ("groups", world_size, self.level_group_size)
+        cached = getattr(self, "_groups_cache", None)
+        if cached is not None and cached[0] == key:
+            return cached[1]
+        levels = self.backend.scatter_levels() if (world_size > 1 and hasattr(self.backend, "scatter_levels")) else []
+        groups = []
+        if len(levels) >= 2 and self.level_group_size > 0:
+            cuts = list(range(len(levels), 0, -self.level_group_size))[::-1][-4:]      # at most four: L - 9, L - 6, L - 3, L
+            first_table = min(s for s in self.backend.segments[1:] if s >= 0)
+            lo = 0
+            for hi in cuts:
+                begin = first_table if lo == 0 else levels[lo][0]
+                end = self.backend.fused_count if hi == len(levels) else levels[hi][0]
+                groups.append((lo, hi, begin, end))
+                lo = hi
+        self._groups_cache = (key, groups)
+        return groups
+
     def collectives_per_step(self, world_size: int) -> int:
         """Number of all-reduce calls one step issues at this world size."""
         if world_size <= 1:
             return 0
         table_starts = [s for s in self.backend.segments[1:] if s >= 0]
+        groups = self._level_groups(world_size) if table_starts else []
+        if groups:
+            return len(groups) + 1
         return 2 if (table_starts and getattr(self.backend, "split_gradients", False)) else 1
 
     def state_dict(self):
@@ -151,7 +191,21 @@ class FusedTrainer:
         if global_points is None:
             global_points = world * x.shape[0]
         table_starts = [s for s in self.backend.segments[1:] if s >= 0]
-        if world > 1 and table_starts and getattr(self.backend, "split_gradients", False):
+        groups = self._level_groups(world) if world > 1 and table_starts else []
+        if groups:
+            # The scatter kernel works through the grid levels in a few launches. The gradient of a level is final when
+            # its launch is: its all-reduce starts then (on the communication stream) and runs underneath the scatter of
+            # the following levels, the last one underneath the layers' weight-gradient kernel.
+            self.backend.gradients(x, target, global_points, self.loss_sum, parts=4)
+            pending = []
+            for level_begin, level_end, begin, end in groups:
+                self.backend.gradients(x, target, global_points, self.loss_sum, parts=8 | (level_begin << 8) | (level_end << 16))
+                pending.append(dist.all_reduce(self.gradient[begin:end], op=dist.ReduceOp.SUM, group=self.process_group, async_op=True))
+            self.backend.gradients(x, target, global_points, self.loss_sum, parts=2)
+            dist.all_reduce(self.gradient[:groups[0][2]], op=dist.ReduceOp.SUM, group=self.process_group)
+            for p in pending:
+                p.wait()
+        elif world > 1 and table_starts and getattr(self.backend, "split_gradients", False):
             # The table gradients (nearly all of the vector) are final before the layers' weight gradients are computed:
             # their all-reduce runs on the communication stream underneath the weight-gradient kernel.
             first = min(table_starts)

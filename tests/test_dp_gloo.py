@@ -42,8 +42,38 @@ class OracleStep:
 
     split_gradients = True
 
+    def scatter_levels(self):
+        """Element ranges of the grid levels in the fused buffers, as qmlp_trainer_scatter_levels reports them."""
+        out = []
+        for seg, e in zip(self.segments[1:], self.spec.encodings):
+            for i, lv in enumerate(e.levels):
+                end = e.levels[i + 1].memory_offset if i + 1 < len(e.levels) else e.num_parameters
+                out.append((seg + lv.memory_offset, seg + end))
+        return out
+
     def gradients(self, x, target, global_points, loss_sum, parts=3):
-        """parts as in qmlp_trainer_gradients_part: 1 = up to the table gradients, 2 = the layers' weight gradients."""
+        """parts as in qmlp_trainer_gradients_part: 1 = up to the table gradients, 2 = the layers' weight gradients,
+        4 = forward and backward with the scatter deferred, 8 | first << 8 | end << 16 = scatter of a level range."""
+        what, first, end = parts & 0xff, (parts >> 8) & 0xff, (parts >> 16) & 0xff
+        if what in (4, 8):
+            if what == 4:
+                w, t = self._views(self.half.float())
+                out = oracle.network_forward(self.spec, w, x.numpy(), t)
+                adj = oracle.mse_loss_grad(out, target.numpy(), global_points)
+                self._pending = oracle.network_backward(self.spec, w, x.numpy(), adj, t, want_input=False)
+                loss_sum += float(((out - target.numpy()) ** 2).sum())
+                self._scattered = []
+            else:
+                ranges = self.scatter_levels()[first:end]
+                flat = np.zeros(self.fused_count, dtype=np.float32)
+                for seg, g in zip(self.segments[1:], self._pending.grad_encodings):
+                    if g is not None:
+                        flat[seg:seg + g.size] = g
+                for b, e in ranges:
+                    self.grad[b:e] += torch_from(flat[b:e])
+                self._scattered += list(range(first, end))
+            self.parts_seen = getattr(self, "parts_seen", []) + [parts]
+            return
         if parts & 1:
             w, t = self._views(self.half.float())
             out = oracle.network_forward(self.spec, w, x.numpy(), t)
@@ -64,6 +94,11 @@ class OracleStep:
         oracle.adam_step(self.master.numpy(), self.grad.numpy() * grad_scale, self.m.numpy(), self.v.numpy(), step)
         self.grad.zero_()
         self.refresh_half()
+
+
+def torch_from(a):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(a))
 
 
 def _cfg():
@@ -105,6 +140,11 @@ def _train(rank, world, x, t, steps):
     b, e = shard_points(x.shape[0], rank, world)
     for _ in range(steps):
         tr.step(torch.from_numpy(x[b:e]), torch.from_numpy(t[b:e]), global_points=x.shape[0])
+    if world > 1:
+        # the data-parallel step cut the scatter into level groups, each followed by its own all-reduce
+        seen = [p & 0xff for p in backend.parts_seen]
+        assert seen.count(4) == steps and seen.count(8) == steps * len(tr._level_groups(world)) and seen.count(2) == steps
+        assert sorted(backend._scattered) == list(range(len(backend.scatter_levels())))
     return tr.master.numpy().copy(), tr.mean_loss(x.shape[0] * steps)
 
 
