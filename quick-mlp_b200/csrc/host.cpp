@@ -6,7 +6,7 @@
 #include <cstring>
 #include <fstream>
 #include <random>
-#include <regex>
+#include <cctype>
 #include <set>
 #include <sstream>
 #include <sys/stat.h>
@@ -71,8 +71,12 @@ Activation::Activation(const std::string& id, const std::string& forward, const 
     : id_(id), forward_(forward), adjoint_(adjoint)
 {
     // src_cpp/src/activation.cpp:31-37
-    static const std::regex CPP_IDENTIFIER("^[a-zA-Z_][a-zA-Z0-9_]*$");
-    if (!std::regex_match(id, CPP_IDENTIFIER))
+    // (checked by hand rather than with std::regex: its template instances carry process-wide "unique" symbols, and in a
+    // process that holds a second copy of the C++ runtime - an extension module linked against a static libstdc++ is
+    // enough - the tables of the two get mixed and regex_match crashes)
+    bool identifier = !id.empty() && (std::isalpha(static_cast<unsigned char>(id[0])) || id[0] == '_');
+    for (char c : id) identifier = identifier && (std::isalnum(static_cast<unsigned char>(c)) || c == '_');
+    if (!identifier)
         throw configuration_error(format("id of the activation function is not a valid C++ identifier: %s", id.c_str()));
     builtin_ = builtinFunctorFor(forward, adjoint) != nullptr;
 }

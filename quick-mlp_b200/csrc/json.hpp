@@ -133,8 +133,12 @@ private:
         case Null: o << "null"; break;
         case Bool: o << (bool_ ? "true" : "false"); break;
         case Number:
-            if (isInt_) o << static_cast<long long>(num_);
-            else { char b[40]; std::snprintf(b, sizeof b, "%.9g", num_); o << b; }
+            // formatted with snprintf, not with the stream's numeric inserter: that one goes through locale facets, which
+            // fail in a process that holds a second copy of the C++ runtime (an extension linked against a static libstdc++)
+            char b[40];
+            if (isInt_) std::snprintf(b, sizeof b, "%lld", static_cast<long long>(num_));
+            else std::snprintf(b, sizeof b, "%.9g", num_);
+            o << b;
             break;
         case String: writeString(o, str_); break;
         case Array: {
