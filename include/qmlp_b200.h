@@ -90,14 +90,21 @@ QMLP_API int qmlp_set_kernel_include_dir(const char* dir);
  * reference's per-kernel tuning options (overwrite_blocksize_*, skew_shared_memory;
  * src_cpp/src/fused_network.cpp:45-69). */
 QMLP_API int qmlp_set_kernel_path(int path);
-/* Synchronises the current device and returns (then clears) its kernel status word: 0 = every kernel ran to completion,
- * 1 = a kernel gave up on a bounded on-chip wait and its results are invalid. The reference has no counterpart (its
+/* Synchronises the current device and returns (then clears) its kernel status word: 0 = every kernel ran to completion;
+ * bit 0 (1) = a kernel gave up on a bounded on-chip wait and its results are invalid; bits 1, 2, 3 (2, 4, 8) = a kernel
+ * instantiated with bounds checks (qmlp_set_tuning("bounds_check", 1)) met a table row, a stash offset or a plane offset
+ * outside the size the host declared and skipped that access. The reference has no counterpart (its
  * kernels contain no waits); debugging aids there are printf paths (src_cpp/include/qmlp/kernels/layer.cuh:28-41). */
 QMLP_API int qmlp_device_status(int* status);
 /* Tuning switches of the fused training step, for measurements; -1 restores the library's own choice.
  * "sort_points": copy a batch into spatial-bin order first (1; never chosen automatically: it loses on random batches); "split_scatter": table-gradient scatter as
  * its own kernel (1) or inside the backward kernel (0); "scatter_runs": 0 sends every table-gradient contribution of
- * the sorted scatter straight to the table instead of summing runs of points that share a cell first. Stand in for the reference's tuning options
+ * the sorted scatter straight to the table instead of summing runs of points that share a cell first. "bounds_check": 1
+ * makes networks and encodings use (and build, on first use) instantiations whose kernels test every table row, stash
+ * offset and plane offset against the declared sizes, skip what lies outside and set a bit of the status word
+ * (qmlp_device_status) instead of faulting - the role of the reference's debug asserts in WrappedArray
+ * (src_cpp/include/qmlp/kernels/common.cuh:174-218); "bounds_shrink": n declares every size n elements smaller than it
+ * is (test hook: the check fires while every access still lands in real memory). Stand in for the reference's tuning options
  * (src_cpp/src/fused_network.cpp:45-69). */
 QMLP_API int qmlp_set_tuning(const char* key, int value);
 /* Per-kernel device timing: while enabled, every kernel the library launches is bracketed by a CUDA event pair on its

@@ -81,6 +81,7 @@ void fillCommon(Network& n, kernel::LaunchArgs& a, const qmlp_tensor_t* input)
     a.forcePath = Library::instance().kernelPath;
     a.status = Library::instance().statusWord();
     n.fillGrids(a);
+    for (int i = 0; i < a.numGrids; ++i) a.grids[i].status = a.status;
     for (int i = 0; i < n.numEncodings(); ++i) {
         auto e = n.encoding(i);
         if (e->hasParameters() && !e->paramInference.defined())
@@ -130,11 +131,25 @@ struct TimedLaunch {
     }
 };
 
+// The launch arguments with the sizes of the scratch buffers they point to, for bounds-checking instantiations: the stash
+// and the delta stash hold n32 rows of the network's widths, the planes planeStride points of the encoded channels.
+kernel::LaunchArgs withScratchSizes(const Network& n, const kernel::LaunchArgs& a)
+{
+    kernel::LaunchArgs b = a;
+    const long long n32 = (a.numel + 31) / 32 * 32;
+    const long long shrink = Library::instance().boundsShrink;
+    b.fwdTmpHalfs = a.fwdTmp ? std::max<long long>(1, n32 * n.stashHalfsPerPoint() - shrink) : 0;
+    b.adjTmpHalfs = a.adjTmp ? std::max<long long>(1, n32 * n.deltaHalfsPerPoint() - shrink) : 0;
+    b.planeHalfs = a.planes ? std::max<long long>(1, a.planeStride * n.encodedChannels() - shrink) : 0;
+    return b;
+}
+
 void launchModule(Network& n, KernelModule& m, int kernelId, const kernel::LaunchArgs& a, qmlp_stream_t stream)
 {
     TimedLaunch timed(kernelId, static_cast<cudaStream_t>(stream));
     int launches = 0;
-    checkLaunch(m.launch(kernelId, &a, static_cast<cudaStream_t>(stream), &launches), "kernel launch failed");
+    const kernel::LaunchArgs b = withScratchSizes(n, a);
+    checkLaunch(m.launch(kernelId, &b, static_cast<cudaStream_t>(stream), &launches), "kernel launch failed");
     n.launchCount += launches;
 }
 
@@ -271,7 +286,9 @@ int qmlp_set_tuning(const char* key, int value)
     if (k == "sort_points") lib.sortPoints = value;
     else if (k == "split_scatter") lib.splitScatter = value;
     else if (k == "scatter_runs") lib.runAggregation = value;
-    else throw std::runtime_error("unknown tuning key '" + k + "' (sort_points, split_scatter, scatter_runs)");
+    else if (k == "bounds_check") lib.boundsCheck = value > 0;
+    else if (k == "bounds_shrink") lib.boundsShrink = value > 0 ? value : 0;
+    else throw std::runtime_error("unknown tuning key '" + k + "' (sort_points, split_scatter, scatter_runs, bounds_check, bounds_shrink)");
     QMLP_CATCH
 }
 
@@ -461,7 +478,8 @@ static void inferenceLocked(Network& n, const qmlp_tensor_t* input, qmlp_tensor_
             int e;
             {
                 TimedLaunch timed(kernel::KERNEL_ENCODE_PLANES, static_cast<cudaStream_t>(stream));
-                e = m->launch(kernel::KERNEL_ENCODE_PLANES, &a, static_cast<cudaStream_t>(stream), &launches);
+                const kernel::LaunchArgs sized = withScratchSizes(n, a);
+                e = m->launch(kernel::KERNEL_ENCODE_PLANES, &sized, static_cast<cudaStream_t>(stream), &launches);
             }
             if (e == static_cast<int>(cudaErrorNotSupported) && c0 == 0) { n.planesUnsupported = true; ok = false; break; }
             checkLaunch(e, "kernel launch failed");
@@ -1102,7 +1120,8 @@ int qmlp_trainer_gradients_part(qmlp_trainer_t* tr, const qmlp_tensor_t* input, 
             int e;
             {
                 TimedLaunch timed(kernel::KERNEL_ENCODE_PLANES, static_cast<cudaStream_t>(stream));
-                e = m->launch(kernel::KERNEL_ENCODE_PLANES, &a, static_cast<cudaStream_t>(stream), &launches);
+                const kernel::LaunchArgs sized = withScratchSizes(n, a);
+                e = m->launch(kernel::KERNEL_ENCODE_PLANES, &sized, static_cast<cudaStream_t>(stream), &launches);
             }
             if (e == static_cast<int>(cudaErrorNotSupported)) {
                 n.planesUnsupported = true;

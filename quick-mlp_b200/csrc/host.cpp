@@ -198,7 +198,7 @@ void Encoding::setParameter(const qmlp_tensor_t*, int) {}
 
 std::shared_ptr<KernelModule> Encoding::standaloneModule(bool halfTable)
 {
-    auto& m = standalone_[halfTable ? 1 : 0];
+    auto& m = standalone_[(halfTable ? 1 : 0) + (Library::instance().boundsCheck ? 2 : 0)];
     if (m) return m;
     std::ostringstream s;
     s << "// stand-alone encoding kernels: " << toJson().dump() << "\n#include \"standalone.cuh\"\nusing namespace qmlp::kernel;\n"
@@ -341,6 +341,11 @@ void EncodingHashGrid::fillGrid(kernel::GridP& g) const
         g.boxSize[i] = i < dim_ ? boxSize_[i] : 1.f;
     }
     g.stepsize = 0.f;
+    // what bounds-checking instantiations compare every row against (boundsShrink: a test hook that declares the table
+    // smaller than it is, so that the check can be seen to fire without any access leaving the real table)
+    const int64_t shrink = Library::instance().boundsShrink;
+    g.tableCount = static_cast<unsigned long long>(std::max<int64_t>(0, numParameters_ - shrink));
+    g.status = nullptr;
     for (int l = 0; l < levels_; ++l) {
         g.levels[l].offset = static_cast<unsigned int>(table_[l].memoryOffset);
         g.levels[l].resolution = table_[l].resolution;
@@ -768,10 +773,12 @@ std::string Network::generateSource(unsigned halfMask) const
 
 std::shared_ptr<KernelModule> Network::module(unsigned halfMask)
 {
-    auto it = modules_.find(halfMask);
+    // bounds-checking instantiations are separate shared objects: bit 31 of the cache key
+    const unsigned key = halfMask | (Library::instance().boundsCheck ? 0x80000000u : 0u);
+    auto it = modules_.find(key);
     if (it != modules_.end()) return it->second;
     auto m = getKernelModule("net", generateSource(halfMask));
-    modules_[halfMask] = m;
+    modules_[key] = m;
     return m;
 }
 

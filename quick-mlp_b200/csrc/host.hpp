@@ -48,6 +48,10 @@ struct Library {
     int sortPoints = -1;      // spatially sorted step (kernels/sorted_scatter.cuh): 1 on whenever instantiated, else off
     int splitScatter = -1;    // table-gradient scatter as its own kernel: 0 inside the backward kernel, 1 separate
     int runAggregation = 1;   // coarse levels of the sorted scatter: corner sums of a run of points in one cell kept in registers
+    // kernels instantiated with QMLP_BOUNDS_CHECK: every table row, stash offset and plane offset is tested against the
+    // size the host declares; an access outside is skipped and reported through the status word
+    bool boundsCheck = false;
+    int64_t boundsShrink = 0; // test hook: declare tables and scratch buffers this many elements smaller than they are
     int* statusWord();     // device word of the current device that kernels set when a bounded wait gives up
 };
 
@@ -126,7 +130,7 @@ public:
     std::string jsonCache, idCache;
 
 private:
-    std::shared_ptr<KernelModule> standalone_[2];
+    std::shared_ptr<KernelModule> standalone_[4];   // [fp32 | fp16 table] x [regular | bounds-checking]
 };
 typedef std::shared_ptr<Encoding> Encoding_ptr;
 

@@ -181,6 +181,7 @@ std::shared_ptr<KernelModule> getKernelModule(const std::string& kind, const std
     const std::string cache = lib.resolveCacheDir();
     uint64_t h = fnv1a(source, headersDigest(inc));
     h = fnv1a(lib.debugMode ? "debug" : "release", h);
+    if (lib.boundsCheck) h = fnv1a("bounds-check", h);
     h = fnv1a(std::to_string(QMLP_SPEC_ABI_VERSION), h);
     char hex[32];
     std::snprintf(hex, sizeof hex, "%016llx", static_cast<unsigned long long>(h));
@@ -214,7 +215,7 @@ std::shared_ptr<KernelModule> getKernelModule(const std::string& kind, const std
         }
         std::ostringstream cmd;
         cmd << nvcc << " -std=c++17 -gencode arch=compute_100a,code=sm_100a -lineinfo "
-            << (lib.debugMode ? "-O0 -G " : "-O3 ") << "-shared -Xcompiler -fPIC -I'" << inc << "' -o '" << tmp << "' '" << cu
+            << (lib.debugMode ? "-O0 -G " : "-O3 ") << (lib.boundsCheck ? "-DQMLP_BOUNDS_CHECK " : "") << "-shared -Xcompiler -fPIC -I'" << inc << "' -o '" << tmp << "' '" << cu
             << "' > '" << log << "' 2>&1";
         logMessage(1, "instantiating kernels for a new spec: " + name + " (nvcc, this takes a few seconds)");
         const int rc = std::system(cmd.str().c_str());

@@ -474,7 +474,7 @@ fused_forward_tc_kernel(const __grid_constant__ LaunchArgs p)
         tc_fence_after();
         tmem_dealloc(tmemBase, TL::tmemCols());
     }
-    if (threadIdx.x == 0 && *abortFlag && p.status != nullptr) atomicExch(p.status, 1);
+    if (threadIdx.x == 0 && *abortFlag && p.status != nullptr) atomicOr(p.status, STATUS_WAIT_TIMEOUT);
 }
 
 template <class Spec>

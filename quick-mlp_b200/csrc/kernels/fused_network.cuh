@@ -108,6 +108,20 @@ __host__ __device__ __forceinline__ long long stash_block(long long tileRow0, in
     return tileRow0 * channels + (cb * 4 + rb) * 64;
 }
 
+// QMLP_BOUNDS_CHECK builds: does [offset, offset + count) lie inside a scratch buffer of `capacity` halfs (0: the host gave
+// no size)? If not, the status word gets `bit` and the caller skips the access. Compiles to `true` in regular builds.
+__device__ __forceinline__ bool scratch_ok(const LaunchArgs& p, long long offset, int count, long long capacity, int bit)
+{
+    if constexpr (BOUNDS_CHECK) {
+        if (capacity > 0 && (offset < 0 || offset + count > capacity)) {
+            if (p.status != nullptr) atomicOr(p.status, bit);
+            return false;
+        }
+    }
+    (void)p; (void)offset; (void)count; (void)capacity; (void)bit;
+    return true;
+}
+
 // CTAs per SM the forward and backward kernels are compiled for: two (a 128-register budget per thread, which costs
 // the 128-wide networks a few dozen bytes of spills but doubles the warps that hide gather and stash latency) whenever
 // two copies of the shared-memory plan fit on an SM, else one.
@@ -321,15 +335,26 @@ __device__ __forceinline__ void read_planes_point(const LaunchArgs& p, long long
         using Enc = typename Spec::template Enc<E>;
         if constexpr (!Enc::IS_GRID) {
             const __half* src = p.planes + p.planeStride * Enc::OUT_OFF + local * Enc::N;
+            const bool ok = scratch_ok(p, src - p.planes, Enc::N, p.planeHalfs, STATUS_PLANES);
             __half v[Enc::N];
 #pragma unroll
-            for (int i = 0; i < Enc::N; ++i) v[i] = __ldg(src + i);
+            for (int i = 0; i < Enc::N; ++i) v[i] = ok ? __ldg(src + i) : __ushort_as_half(0);
 #pragma unroll
             for (int i = 0; i < Enc::N; ++i) out.half(Enc::OUT_OFF + i, v[i]);
         } else {
             constexpr int GROUPS = Enc::CONCAT ? Enc::L : 1;
             constexpr int F = Enc::F;
             const __half* base = p.planes + p.planeStride * Enc::OUT_OFF + local * F;
+            if constexpr (BOUNDS_CHECK) {
+                // the planes of this encoding's levels: first and last one read below
+                if (!scratch_ok(p, base - p.planes, F, p.planeHalfs, STATUS_PLANES) ||
+                    !scratch_ok(p, (base - p.planes) + p.planeStride * ((GROUPS - 1) * F), F, p.planeHalfs, STATUS_PLANES)) {
+#pragma unroll
+                    for (int i = 0; i < GROUPS * F; ++i) out.half(Enc::OUT_OFF + i, __ushort_as_half(0));
+                    read_planes_point<Spec, E + 1, Out>(p, local, out);
+                    return;
+                }
+            }
             if constexpr (F == 2) {
                 uint32_t v[GROUPS];
 #pragma unroll
@@ -435,10 +460,11 @@ __device__ __forceinline__ void forward_layers(const LaunchArgs& p, const __half
                 __half* st = p.fwdTmp + n32 * SL::preOffset(L) + (r * 8 + q * 2);
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    if (row0 < p.numel)
-                        *reinterpret_cast<__half2*>(st + stash_block(rowBase, COUT, m * 2, j * 2 + h)) = pre[h][0];
-                    if (row0 + 8 < p.numel)
-                        *reinterpret_cast<__half2*>(st + stash_block(rowBase, COUT, m * 2 + 1, j * 2 + h)) = pre[h][1];
+                    const long long lo = stash_block(rowBase, COUT, m * 2, j * 2 + h), hi = stash_block(rowBase, COUT, m * 2 + 1, j * 2 + h);
+                    if (row0 < p.numel && scratch_ok(p, (st - p.fwdTmp) + lo, 2, p.fwdTmpHalfs, STATUS_STASH))
+                        *reinterpret_cast<__half2*>(st + lo) = pre[h][0];
+                    if (row0 + 8 < p.numel && scratch_ok(p, (st - p.fwdTmp) + hi, 2, p.fwdTmpHalfs, STATUS_STASH))
+                        *reinterpret_cast<__half2*>(st + hi) = pre[h][1];
                 }
             }
 #pragma unroll
@@ -522,7 +548,7 @@ fused_forward_kernel(const __grid_constant__ LaunchArgs p)
             __half* st = p.fwdTmp; // offset 0
             for (int i = lane; i < TILE_POINTS * CH; i += 32) {
                 const int rr = i / CH, cc = i % CH;
-                if (rowBase + rr < p.numel)
+                if (rowBase + rr < p.numel && scratch_ok(p, (rowBase + rr) * CIN0 + cc * 8, 8, p.fwdTmpHalfs, STATUS_STASH))
                     *reinterpret_cast<uint4*>(st + (rowBase + rr) * CIN0 + cc * 8) = *reinterpret_cast<const uint4*>(tile + rr * TS + cc * 8);
             }
         }
@@ -600,6 +626,7 @@ __device__ __forceinline__ void write_adjoint_planes(const LaunchArgs& p, long l
                 constexpr int F = Enc::F;
                 const int c0 = Enc::OUT_OFF + l * F;
                 __half* dst = p.planes + p.planeStride * c0 + point * F;
+                if (!scratch_ok(p, dst - p.planes, F, p.planeHalfs, STATUS_PLANES)) continue;
                 if constexpr (F % 2 == 0) {
                     uint32_t w[F / 2];
 #pragma unroll
@@ -653,7 +680,8 @@ __device__ __forceinline__ void backward_layers(const LaunchArgs& p, const __hal
             for (int e = 0; e < 4; ++e) {
                 const long long row = rowBase + m * 16 + r + (e & 1) * 8;
                 const long long at = stash_block(rowBase, COUT, m * 2 + (e & 1), k * 2 + (e >> 1)) + (r * 8 + q * 2);
-                x[k][e] = row < p.numel ? __ldg(reinterpret_cast<const unsigned int*>(pre + at)) : 0u;
+                const bool ok = row < p.numel && scratch_ok(p, (pre - p.fwdTmp) + at, 2, p.fwdTmpHalfs, STATUS_STASH);
+                x[k][e] = ok ? __ldg(reinterpret_cast<const unsigned int*>(pre + at)) : 0u;
             }
 #pragma unroll
         for (int k = 0; k < KT; ++k)
@@ -665,7 +693,8 @@ __device__ __forceinline__ void backward_layers(const LaunchArgs& p, const __hal
                 const __half2 d = act_adjoint2<Act>(u32_as_h2(x[k][e]), u32_as_h2(adj[m][k][e]), col);
                 adj[m][k][e] = h2_as_u32(d);
                 if constexpr ((FLAGS & FLAG_GRAD_WEIGHTS) != 0) {
-                    if (row < p.numel) *reinterpret_cast<__half2*>(dl + at) = d;
+                    if (row < p.numel && scratch_ok(p, (dl - p.adjTmp) + at, 2, p.adjTmpHalfs, STATUS_STASH))
+                        *reinterpret_cast<__half2*>(dl + at) = d;
                 }
             }
     }
@@ -886,17 +915,17 @@ __device__ __forceinline__ void wgrad_layer(const LaunchArgs& p, unsigned char* 
         // ldmatrix matrix reads (no bank conflicts, no padding). The encoded input (L == 0) is row-major with padded rows.
         for (int i = threadIdx.x; i < SLAB * DCH; i += WG_WARPS * 32) {
             const int rr = (i / (32 * DCH)) * 32 + (i % 32);        // the point of piece i (storage order)
-            const bool ok = row0 + rr < p.numel;
+            const bool ok = row0 + rr < p.numel && scratch_ok(p, (gD - p.adjTmp) + row0 * COUT + i * 8, 8, p.adjTmpHalfs, STATUS_STASH);
             cp_async16(smem_u32(sDbase + buf * STAGE_HALFS + i * 8), gD + (ok ? row0 * COUT + i * 8 : 0), ok);
         }
         for (int i = threadIdx.x; i < SLAB * ACH; i += WG_WARPS * 32) {
             if constexpr (L == 0) {
                 const int rr = i / ACH, cc = i % ACH;
-                const bool ok = row0 + rr < p.numel;
+                const bool ok = row0 + rr < p.numel && scratch_ok(p, (gA - p.fwdTmp) + (row0 + rr) * CIN + cc * 8, 8, p.fwdTmpHalfs, STATUS_STASH);
                 cp_async16(smem_u32(sAbase + buf * STAGE_HALFS + rr * BS + cc * 8), gA + (ok ? row0 + rr : 0) * CIN + cc * 8, ok);
             } else {
                 const int rr = (i / (32 * ACH)) * 32 + (i % 32);
-                const bool ok = row0 + rr < p.numel;
+                const bool ok = row0 + rr < p.numel && scratch_ok(p, (gA - p.fwdTmp) + row0 * CIN + i * 8, 8, p.fwdTmpHalfs, STATUS_STASH);
                 cp_async16(smem_u32(sAbase + buf * STAGE_HALFS + i * 8), gA + (ok ? row0 * CIN + i * 8 : 0), ok);
             }
         }

@@ -58,14 +58,23 @@ __device__ __forceinline__ unsigned int grid_vertex_index(const unsigned int (&v
     return idx * F + lv.offset;
 }
 
-// Element index of corner `bits` of a cell (bit k set -> high corner in dimension k).
+// Element index of corner `bits` of a cell (bit k set -> high corner in dimension k). Every table access of every kernel
+// takes its index from here, so this is where a QMLP_BOUNDS_CHECK build tests it: a row that does not lie inside the
+// table is reported through the status word and replaced by row 0 of the table, and the kernel carries on.
 template <int D, int F>
-__device__ __forceinline__ unsigned int grid_corner_index(const GridCell<D>& c, const GridLevelP& lv, int bits)
+__device__ __forceinline__ unsigned int grid_corner_index(const GridP& g, const GridCell<D>& c, const GridLevelP& lv, int bits)
 {
     unsigned int v[D];
 #pragma unroll
     for (int k = 0; k < D; ++k) v[k] = ((bits >> k) & 1) ? c.hi[k] : c.lo[k];
-    return grid_vertex_index<D, F>(v, lv);
+    const unsigned int e = grid_vertex_index<D, F>(v, lv);
+    if constexpr (BOUNDS_CHECK) {
+        if (static_cast<unsigned long long>(e) + F > g.tableCount) {
+            if (g.status != nullptr) atomicOr(g.status, STATUS_TABLE_ROW);
+            return 0u;
+        }
+    }
+    return e;
 }
 
 // encoding_hashgrid.cuh:177-185,209-215: product taken from dimension D-1 down to 0
@@ -163,7 +172,7 @@ __device__ __forceinline__ void grid_level_forward(const GridP& g, const GridLev
             uint32_t raw[1 << D][F / 2];
 #pragma unroll
             for (int b = 0; b < (1 << D); ++b) {
-                const __half* t = static_cast<const __half*>(g.table) + grid_corner_index<D, F>(c, lv, b);
+                const __half* t = static_cast<const __half*>(g.table) + grid_corner_index<D, F>(g, c, lv, b);
                 if constexpr (F == 2) {
                     raw[b][0] = ldg_nc_u32(t);
                 } else if constexpr (F == 4) {
@@ -192,7 +201,7 @@ __device__ __forceinline__ void grid_level_forward(const GridP& g, const GridLev
     float rows[1 << D][F];
     // issue every corner load before the blend so they are all in flight together
 #pragma unroll
-    for (int b = 0; b < (1 << D); ++b) grid_load_row<F, HALF>(g.table, grid_corner_index<D, F>(c, lv, b), vec, rows[b]);
+    for (int b = 0; b < (1 << D); ++b) grid_load_row<F, HALF>(g.table, grid_corner_index<D, F>(g, c, lv, b), vec, rows[b]);
 #pragma unroll
     for (int i = 0; i < F; ++i) feat[i] = 0.f;
 #pragma unroll
@@ -218,7 +227,7 @@ __device__ __forceinline__ void grid_level_adjoint(const GridP& g, const GridLev
     for (int k = 0; k < D; ++k) lvl[k] = 0.f;
 #pragma unroll
     for (int b = 0; b < (1 << D); ++b) {
-        const unsigned int e = grid_corner_index<D, F>(c, lv, b);
+        const unsigned int e = grid_corner_index<D, F>(g, c, lv, b);
         if constexpr (PARAM_GRAD) grid_scatter_row<F>(g.grad, e, vec, grid_corner_weight<D>(c, b), adjF);
         if constexpr (INPUT_GRAD) {
             float row[F];
@@ -262,7 +271,7 @@ __device__ __forceinline__ void grid_level_scatter_paired(const GridP& g, const 
             for (int h = 0; h < (1 << (D - 1)); ++h) {
                 const int b0 = pd == 0 ? (h << 1) : h;
                 const int b1 = b0 | (1 << pd);
-                const unsigned int eA = grid_corner_index<D, F>(c, lv, b0), eB = grid_corner_index<D, F>(c, lv, b1);
+                const unsigned int eA = grid_corner_index<D, F>(g, c, lv, b0), eB = grid_corner_index<D, F>(g, c, lv, b1);
                 const float wA = grid_corner_weight<D>(c, b0), wB = grid_corner_weight<D>(c, b1);
                 float* pa = g.grad + eA;
                 float* pb = g.grad + eB;
@@ -282,7 +291,7 @@ __device__ __forceinline__ void grid_level_scatter_paired(const GridP& g, const 
     }
 #pragma unroll
     for (int b = 0; b < (1 << D); ++b)
-        grid_scatter_row<F>(g.grad, grid_corner_index<D, F>(c, lv, b), vec, grid_corner_weight<D>(c, b), adjF);
+        grid_scatter_row<F>(g.grad, grid_corner_index<D, F>(g, c, lv, b), vec, grid_corner_weight<D>(c, b), adjF);
 }
 
 } // namespace kernel

@@ -38,8 +38,9 @@ __host__ __device__ constexpr int plane_group_count()
 }
 
 template <int W>
-__device__ __forceinline__ void store_halfs(__half* dst, const float (&v)[W])
+__device__ __forceinline__ void store_halfs(const LaunchArgs& p, __half* dst, const float (&v)[W])
 {
+    if (!scratch_ok(p, dst - p.planes, W, p.planeHalfs, STATUS_PLANES)) return;
     if constexpr (W == 2) {
         *reinterpret_cast<__half2*>(dst) = __floats2half2_rn(v[0], v[1]);
     } else if constexpr (W == 4) {
@@ -75,7 +76,7 @@ __device__ __forceinline__ void encode_group(const LaunchArgs& p, int g, const R
             float v[Enc::N];
 #pragma unroll
             for (int i = 0; i < Enc::N; ++i) v[i] = in(i + Enc::START);
-            store_halfs<Enc::N>(p.planes + p.planeStride * Enc::OUT_OFF + local * Enc::N, v);
+            store_halfs<Enc::N>(p, p.planes + p.planeStride * Enc::OUT_OFF + local * Enc::N, v);
         } else {
             const GridP& grid = p.grids[Enc::SLOT];
             float pos[Enc::D];
@@ -84,7 +85,7 @@ __device__ __forceinline__ void encode_group(const LaunchArgs& p, int g, const R
             if constexpr (Enc::CONCAT) {
                 const int l = g - PG::before();
                 grid_level_forward<Enc::D, Enc::F, Enc::HALF_TABLE>(grid, grid.levels[l], pos, feat);
-                store_halfs<Enc::F>(p.planes + p.planeStride * (Enc::OUT_OFF + l * Enc::F) + local * Enc::F, feat);
+                store_halfs<Enc::F>(p, p.planes + p.planeStride * (Enc::OUT_OFF + l * Enc::F) + local * Enc::F, feat);
             } else {
 #pragma unroll
                 for (int i = 0; i < Enc::F; ++i) feat[i] = 0.f;
@@ -94,7 +95,7 @@ __device__ __forceinline__ void encode_group(const LaunchArgs& p, int g, const R
 #pragma unroll
                     for (int i = 0; i < Enc::F; ++i) feat[i] += f[i];
                 }
-                store_halfs<Enc::F>(p.planes + p.planeStride * Enc::OUT_OFF + local * Enc::F, feat);
+                store_halfs<Enc::F>(p, p.planes + p.planeStride * Enc::OUT_OFF + local * Enc::F, feat);
             }
         }
     }
@@ -176,6 +177,7 @@ __device__ __forceinline__ void scatter_group(const LaunchArgs& p, int g, const 
             const int l = g - SG::before();
             const int c0 = Enc::OUT_OFF + (Enc::CONCAT ? l * Enc::F : 0);
             const __half* src = p.planes + p.planeStride * c0 + point * Enc::F;
+            if (!scratch_ok(p, src - p.planes, Enc::F, p.planeHalfs, STATUS_PLANES)) return;
             float adjF[Enc::F];
             if constexpr (Enc::F == 2) {
                 const float2 x = __half22float2(u32_as_h2(*reinterpret_cast<const uint32_t*>(src)));

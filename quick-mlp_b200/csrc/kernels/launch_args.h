@@ -30,8 +30,20 @@ struct GridP {
     float stepsize;    // line integration only: world-space step along the ray
     int tableIsHalf;
     int vecOk; // table and grad pointers are aligned for whole-row vector access
+    unsigned long long tableCount; // elements of the table (and of its gradient): what QMLP_BOUNDS_CHECK builds check rows against
+    int* status;                   // the library's status word (QMLP_BOUNDS_CHECK builds report through it), may be null
     GridLevelP levels[MAX_GRID_LEVELS];
 };
+
+// Bits of the library's device status word (qmlp_device_status). Bit 0 is set by a kernel that gave up on a bounded wait;
+// the others only by instantiations compiled with QMLP_BOUNDS_CHECK, which test every table row, stash offset and plane
+// offset against the size the host declared, skip an access that would leave it and report here instead of faulting.
+constexpr int STATUS_WAIT_TIMEOUT = 1, STATUS_TABLE_ROW = 2, STATUS_STASH = 4, STATUS_PLANES = 8;
+#ifdef QMLP_BOUNDS_CHECK
+constexpr bool BOUNDS_CHECK = true;
+#else
+constexpr bool BOUNDS_CHECK = false;
+#endif
 
 // bits of LaunchArgs::flags for the backward kernel (AdjointMode of the reference,
 // src_cpp/include/qmlp/fused_network.h:22-34)
@@ -63,6 +75,7 @@ struct LaunchArgs {
     int* status;                                   // device word set to 1 when a kernel gave up on a bounded wait
     __half* planes;                                // encoded features (or their adjoints) of a chunk of points, one plane per grid level
     long long planeStride;                         // points per plane (capacity of the chunk buffer)
+    long long fwdTmpHalfs, adjTmpHalfs, planeHalfs; // sizes of the three scratch buffers in halfs (QMLP_BOUNDS_CHECK builds; 0: unknown)
     // spatially binned training step (kernels/sorted_scatter.cuh): KERNEL_SORT_POINTS copies the points (and targets)
     // into Morton-bin order; the kernels after it read the sorted copies through `input` / `target`
     unsigned int* binCounts;                       // points per bin (sort_bin_count() entries), zeroed by the launcher
@@ -118,4 +131,4 @@ extern "C" {
 typedef int (*qmlp_spec_launch_fn)(int kernel, const void* args, cudaStream_t stream, int* launches);
 typedef int (*qmlp_spec_abi_fn)(void);
 }
-#define QMLP_SPEC_ABI_VERSION 8
+#define QMLP_SPEC_ABI_VERSION 9

@@ -203,7 +203,7 @@ __device__ __forceinline__ void grid_scatter_cell(const GridP& g, const GridLeve
             for (int h = 0; h < (1 << (D - 1)); ++h) {
                 const int b0 = pd == 0 ? (h << 1) : h;
                 const int b1 = b0 | (1 << pd);
-                const unsigned int eA = grid_corner_index<D, F>(c, lv, b0), eB = grid_corner_index<D, F>(c, lv, b1);
+                const unsigned int eA = grid_corner_index<D, F>(g, c, lv, b0), eB = grid_corner_index<D, F>(g, c, lv, b1);
                 // b0 / b1 depend on pd at run time: pick the sums with selects, not with dynamic indexing
                 float a0 = 0.f, a1 = 0.f, c0 = 0.f, c1 = 0.f;
 #pragma unroll
@@ -228,7 +228,7 @@ __device__ __forceinline__ void grid_scatter_cell(const GridP& g, const GridLeve
         }
     }
 #pragma unroll
-    for (int b = 0; b < (1 << D); ++b) grid_scatter_row<F>(g.grad, grid_corner_index<D, F>(c, lv, b), vec, 1.0f, acc[b]);
+    for (int b = 0; b < (1 << D); ++b) grid_scatter_row<F>(g.grad, grid_corner_index<D, F>(g, c, lv, b), vec, 1.0f, acc[b]);
 }
 
 // One grid level of one encoding for the sorted points [base, end) of this CTA.
@@ -251,6 +251,7 @@ __device__ __forceinline__ void scatter_sorted_level(const LaunchArgs& p, const 
         for (long long pt = base + threadIdx.x; pt < end; pt += SORTED_THREADS) {
             RowReader in{p.input + pt * p.inS0, p.inS1};
             float adjF[F], pos[D];
+            if (!scratch_ok(p, (plane - p.planes) + pt * F, F, p.planeHalfs, STATUS_PLANES)) continue;
             read_adjoint_features<F>(plane + pt * F, adjF);
             grid_position<D, Enc::START>(grid, in, pos);
             grid_level_scatter_paired<D, F>(grid, lv, pos, adjF);
@@ -268,6 +269,7 @@ __device__ __forceinline__ void scatter_sorted_level(const LaunchArgs& p, const 
         if (pt >= end) break;
         RowReader in{p.input + pt * p.inS0, p.inS1};
         float adjF[F], pos[D];
+        if (!scratch_ok(p, (plane - p.planes) + pt * F, F, p.planeHalfs, STATUS_PLANES)) continue;
         read_adjoint_features<F>(plane + pt * F, adjF);
         grid_position<D, Enc::START>(grid, in, pos);
         GridCell<D> c;

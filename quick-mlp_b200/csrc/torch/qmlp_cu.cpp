@@ -261,8 +261,10 @@ struct NetworkBindings : torch::CustomClassHolder {
 // inputs: input, network parameters, then one tensor per encoding (empty: no parameters)
 struct NetworkFunction : torch::autograd::Function<NetworkFunction> {
     static Tensor forward(AutogradContext* ctx, const NetworkBindings_ptr& self, int64_t flags, const Tensor& input,
-                          const Tensor& networkParameters, variable_list encodingParameters)
+                          const Tensor& networkParameters, at::TensorList encodingList)
     {
+        // (an at::TensorList argument is what autograd walks for inputs; a std::vector would count as one opaque value)
+        const std::vector<Tensor> encodingParameters(encodingList.begin(), encodingList.end());
         c10::cuda::CUDAGuard guard(input.device());
         const Tensor half = NetworkBindings::toHalf(networkParameters.detach());
         Tensor tmp = torch::empty({static_cast<int64_t>(std::max<size_t>(self->n_->forwardMemory(static_cast<int>(input.size(0)), static_cast<int>(flags)), 16))},
@@ -305,7 +307,7 @@ struct NetworkFunction : torch::autograd::Function<NetworkFunction> {
             }
             for (size_t i = 0; i < enc.size() && i < static_cast<size_t>(self->n_->numEncodings()); ++i) {
                 const bool want = (flags & qmlp::FusedNetwork::GRADIENTS_INPUT_ENCODINGS) && enc[i].defined() && enc[i].numel() > 0 &&
-                                  ctx->needs_input_grad(4 + i);
+                                  ctx->needs_input_grad(2 + i);   // edges are counted over the tensor arguments only
                 if (want) {
                     adjEnc[i] = torch::zeros(enc[i].sizes(), enc[i].options().dtype(torch::kFloat32));
                     self->n_->encoding(static_cast<int>(i))->setParameter(wrap(adjEnc[i]), qmlp::Tensor::GRADIENTS);
@@ -335,7 +337,7 @@ Tensor NetworkBindings::forward(const NetworkBindings_ptr& self, const Tensor& i
     for (const auto& p : encodingParameters)
         if (p.defined() && p.requires_grad()) flags |= qmlp::FusedNetwork::GRADIENTS_INPUT_ENCODINGS;
     if (flags == 0 || !torch::GradMode::is_enabled()) return self->inference(input, networkParameters, encodingParameters);
-    return NetworkFunction::apply(self, flags, input, networkParameters, variable_list(encodingParameters.begin(), encodingParameters.end()));
+    return NetworkFunction::apply(self, flags, input, networkParameters, at::TensorList(encodingParameters));
 }
 
 } // namespace

@@ -1,7 +1,8 @@
 """Instantiates kernel templates for a list of specs ahead of time, several nvcc processes at once.
 The library would build a missing instantiation on first use; doing it here keeps compile time out of the GPU run.
 
-Jobs are tuples ("net", cfg_json, grid_half_mask) | ("enc", cfg_json, half_table) | ("act", key_or_json, 0).
+Jobs are tuples ("net", cfg_json, grid_half_mask) | ("enc", cfg_json, half_table) | ("act", key_or_json, 0); a fourth
+element "bounds" asks for the bounds-checking instantiation.
 """
 import json
 import os
@@ -21,6 +22,7 @@ def run_jobs(jobs):
     for job in jobs:
         try:
             kind = job[0]
+            bindings.QuickMLP.set_tuning("bounds_check", 1 if (len(job) > 3 and job[3] == "bounds") else 0)
             if kind == "net":
                 bindings.Network(job[1]).compile(int(job[2]))
             elif kind == "enc":

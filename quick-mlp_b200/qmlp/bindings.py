@@ -49,7 +49,10 @@ class QuickMLP:
 
     @staticmethod
     def set_tuning(key: str, value: int):
-        """Tuning switches of the fused training step ("sort_points", "split_scatter", "scatter_runs"); -1 = automatic."""
+        """Tuning switches of the fused training step ("sort_points", "split_scatter", "scatter_runs"; -1 = automatic) and
+        of the kernel instantiation ("bounds_check": 1 = kernels that test every table row, stash and plane offset and
+        report through device_status() instead of faulting; "bounds_shrink": test hook, declares all sizes that many
+        elements smaller)."""
         check(lib().qmlp_set_tuning(key.encode(), int(value)))
 
     @staticmethod

@@ -28,6 +28,8 @@ def jobs():
     for d in (2, 4):
         out.append(("net", json.dumps(tt.dims_config(d)), 0))
     import test_gpu_full_size as tf
+    for cfg, mask in tf.bounds_check_jobs():
+        out.append(("net", json.dumps(cfg), mask, "bounds"))
     for cfg in tf.probe_encodings():
         out.append(("enc", json.dumps(cfg), 0))
     for name, cfg in te.encoding_cases().items():

@@ -23,6 +23,11 @@ def probe_encodings():
     return [specs.hashgrid(3, 16, 1, 19, 16, 7006, per_level_scale=1.5), specs.hashgrid(4, 16, 1, 22, 16, 2489)]
 
 
+def bounds_check_jobs():
+    """(configuration, fp16-table mask) of the bounds-checking instantiations the tests below use."""
+    return [(specs.config5(), 1), (specs.config3(), 1), (specs.config4(), 0), (specs.config3(log2_hashmap_size=12), 1)]
+
+
 _cache = {}
 
 
@@ -218,3 +223,115 @@ def test_grid_indices_bit_exact_full_size():
             exact = f.max(axis=1) == 0
             assert exact.sum() > n // 8
             assert np.array_equal(out[exact, li], (rows[exact] - lv.memory_offset).astype(np.float32)), f"level {li}: index mismatch"
+
+
+@pytest.fixture
+def bounds_check():
+    """Kernels instantiated with QMLP_BOUNDS_CHECK for one test: every table row, stash offset and plane offset is tested
+    against the declared size, an access outside is skipped and reported through the status word."""
+    from qmlp import bindings
+    bindings.QuickMLP.set_tuning("bounds_check", 1)
+    yield
+    bindings.QuickMLP.set_tuning("bounds_check", 0)
+    bindings.QuickMLP.set_tuning("bounds_shrink", 0)
+
+
+def test_full_size_cases_under_bounds_check(bounds_check):
+    """The full-size networks once more through bounds-checking kernels: 4-D tables of 2^22 rows (element offsets close to
+    2^28) through the chunked level-major pass, a training step on the 2^19-row tables, forward and adjoint of the
+    two-grid network. No access leaves its buffer (status word 0) and the results are those of the regular kernels."""
+    import ctypes as C
+    import torch
+    from qmlp import _capi, bindings
+    from qmlp._capi import check, lib, wrap
+    from qmlp.trainer import FusedTrainer
+    # inference, 4-D grid, fp16 tables, level-major pass
+    cfg, spec, params, tables = _case("config5")
+    x = torch.from_numpy(helpers.uniform(81, 1, (70_001, 4))).cuda()         # more than one 2^16-point chunk of planes
+    tp = torch.from_numpy(params).cuda()
+    tt = [torch.from_numpy(tables[0]).cuda().half()]
+    checked = bindings.Network(json.dumps(cfg)).inference(x, tp, tt)
+    assert bindings.QuickMLP.device_status() == 0
+    bindings.QuickMLP.set_tuning("bounds_check", 0)
+    regular = bindings.Network(json.dumps(cfg)).inference(x, tp, tt)
+    bindings.QuickMLP.set_tuning("bounds_check", 1)
+    assert torch.equal(checked, regular)
+    del tt, checked, regular
+    # training step, 3-D grid
+    cfg, spec, params, tables = _case("config3")
+    n = 1 << 18
+    gen = torch.Generator(device="cuda"); gen.manual_seed(9)
+    x = torch.rand((n, 3), device="cuda", generator=gen)
+    t = torch.sin(8 * x[:, :1]) * torch.cos(6 * x[:, 1:2]) * torch.sin(4 * x[:, 2:3])
+    grads = []
+    for flag in (1, 0):
+        bindings.QuickMLP.set_tuning("bounds_check", flag)
+        tr = FusedTrainer(bindings.Network(json.dumps(cfg)), grid_half_copy=True)
+        tr.set_parameters(torch.from_numpy(params.astype(np.float32)).cuda(), [torch.from_numpy(tables[0]).cuda()])
+        tr.backend.gradients(x, t, n, tr.loss_sum)
+        torch.cuda.synchronize()
+        assert bindings.QuickMLP.device_status() == 0
+        grads.append(tr.gradient.clone())
+        del tr
+    bindings.QuickMLP.set_tuning("bounds_check", 1)
+    scale = float(grads[1].abs().max())
+    assert float(((grads[0] - grads[1]).abs() > 1e-2 * grads[1].abs() + 2e-3 * scale).float().mean()) <= 1e-4
+    # forward + adjoint, dense + hash grid with four features, fp32 tables
+    cfg, spec, params, tables = _case("config4")
+    n = 4099
+    net = bindings.Network(json.dumps(cfg))
+    tx = torch.from_numpy(helpers.uniform(82, 1, (n, 3))).cuda()
+    tadj = torch.from_numpy(helpers.uniform(82, 2, (n, 4), -1.0, 1.0)).cuda()
+    tp = torch.from_numpy(params).cuda()
+    tt = [torch.from_numpy(tb).cuda() for tb in tables]
+    gw = torch.zeros((spec.num_parameters,), device="cuda")
+    gt = [torch.zeros_like(tb) for tb in tt]
+    check(lib().qmlp_network_set_parameter(net._h, wrap(tp), _capi.QMLP_INFERENCE))
+    check(lib().qmlp_network_set_parameter(net._h, wrap(gw), _capi.QMLP_GRADIENTS))
+    for i, tb in enumerate(tt):
+        net.encoding(i).set_parameter(tb, _capi.QMLP_INFERENCE)
+        net.encoding(i).set_parameter(gt[i], _capi.QMLP_GRADIENTS)
+    out = torch.empty((n, 4), device="cuda")
+    fwd = torch.zeros((net.forward_memory(n),), dtype=torch.uint8, device="cuda")
+    bwd = torch.zeros((max(net.adjoint_memory(n, 7), 16),), dtype=torch.uint8, device="cuda")
+    gx = torch.zeros_like(tx)
+    agx = wrap(gx)
+    check(lib().qmlp_network_forward(net._h, wrap(tx), wrap(out), fwd.data_ptr(), None))
+    check(lib().qmlp_network_adjoint(net._h, wrap(tx), wrap(tadj), 7, C.byref(agx), fwd.data_ptr(), bwd.data_ptr(), None))
+    assert bindings.QuickMLP.device_status() == 0
+    assert float(gw.abs().max()) > 0 and all(float(g.abs().max()) > 0 for g in gt) and float(gx.abs().max()) > 0
+
+
+def test_bounds_check_reports_instead_of_faulting(bounds_check):
+    """With every size declared 3000 elements smaller than it is (test hook), the checks must fire: table rows beyond
+    the declared end, stash and plane offsets beyond theirs. The accesses are skipped, the kernels finish, the status
+    word carries the three bits, and nothing faults (the real buffers are larger than declared)."""
+    import torch
+    from qmlp import bindings
+    from qmlp.trainer import FusedTrainer
+    cfg = specs.config3(log2_hashmap_size=12)
+    spec = oracle.parse_spec(cfg)
+    params = helpers.xavier_parameters(spec, cfg, bias_scale=0.05).astype(np.float32)
+    table = helpers.grid_tables(spec, scale=0.5)[0]
+    n = 8192
+    x = torch.from_numpy(helpers.uniform(83, 1, (n, 3))).cuda()
+    t = torch.from_numpy(helpers.uniform(83, 2, (n, 1), -1.0, 1.0)).cuda()
+    tr = FusedTrainer(bindings.Network(json.dumps(cfg)), grid_half_copy=True)
+    tr.set_parameters(torch.from_numpy(params).cuda(), [torch.from_numpy(table).cuda()])
+    bindings.QuickMLP.set_kernel_path(2)        # level-major gather: the planes are in use
+    try:
+        tr.backend.gradients(x, t, n, tr.loss_sum)
+        assert bindings.QuickMLP.device_status() == 0                      # honest sizes: silent
+        bindings.QuickMLP.set_tuning("bounds_shrink", 3000)
+        tr.gradient.zero_()
+        tr.backend.gradients(x, t, n, tr.loss_sum)
+        status = bindings.QuickMLP.device_status()
+    finally:
+        bindings.QuickMLP.set_kernel_path(0)
+        bindings.QuickMLP.set_tuning("bounds_shrink", 0)
+    assert status & 2, "rows beyond the declared end of the table were not reported"
+    assert status & 4, "stash offsets beyond the declared size were not reported"
+    assert status & 8, "plane offsets beyond the declared size were not reported"
+    assert not (status & 1)
+    assert bool(torch.isfinite(tr.gradient).all())
+    assert bindings.QuickMLP.device_status() == 0                          # reading the word cleared it
