@@ -220,7 +220,7 @@ def _read_stash(spec, fwd_tmp, n):
 
 
 @pytest.mark.parametrize("name", list(network_cases().keys()))
-@pytest.mark.parametrize("n", [32, 513])
+@pytest.mark.parametrize("n", [32, 513, 4100])
 def test_forward_and_adjoint(name, n):
     """forward with stash, then the adjoint with every gradient enabled, through the C ABI.
 
