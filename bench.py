@@ -35,9 +35,27 @@ METRIC = "points/sec inference & training step, hashgrid+64-wide MLP, 1/2/4/8 B2
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 SECONDARY = {"c3": ("c3i", "c2"), "c4": ("c2",)}
 
-# DRAM bytes per point (dram__bytes_read.sum + dram__bytes_write.sum of all kernels of one step or launch, divided by the
-# points of the captured case), from the ncu captures summarised under profiles/; traffic grows in proportion to the points
-MEASURED_TRAFFIC_PER_POINT = {"c2": 14.9}
+
+
+def measured_traffic_per_point():
+    """{workload: {kernel: DRAM bytes per point}} from the table in profiles/dram_traffic.md (dram__bytes_read.sum +
+    dram__bytes_write.sum of ncu captures, divided by the points of the captured case)."""
+    table = {}
+    path = os.path.join(ROOT, "profiles", "dram_traffic.md")
+    if not os.path.exists(path):
+        return table
+    with open(path) as f:
+        for line in f:
+            cells = [c.strip() for c in line.strip().strip("|").split("|")]
+            if len(cells) != 5 or cells[0] in ("workload", "") or set(cells[0]) <= set("-"):
+                continue
+            try:
+                table.setdefault(cells[0], {})[cells[1]] = float(cells[4])
+            except ValueError:
+                continue
+    return table
+
+
 KERNEL_NAMES = {0: "inference", 1: "forward_stash", 2: "forward_loss", 3: "backward", 4: "wgrad", 9: "encode_planes",
                 10: "inference_planes", 11: "scatter_planes", 12: "forward_loss_planes", 13: "sort_points",
                 14: "backward_wgrad", 100: "adam", 101: "refresh_half"}
@@ -578,12 +596,13 @@ def roofline_block(bench, r, fp32_tables):
     w, n, key = r["w"], r["n"], r["key"]
     peaks, src = bench.peaks, bench.peak_source
     kernel_ms = r["kernel_ms"]
+    traffic = {} if fp32_tables else measured_traffic_per_point().get(key, {})
     if w["mode"] == "inference" and w["bytes"] <= 64:
         # the layer chain of an identity-encoded network: tensor bound
         peak_s = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops")))
         peak_b = float(peaks.get("bf16_tflops", peak_s))
         achieved = w["flops"] * n / (kernel_ms * 1e-3) / 1e12
-        per_point = MEASURED_TRAFFIC_PER_POINT.get(key)
+        per_point = traffic.get("inference")
         roof = {"bound": "tensor", "achieved": achieved, "peak": peak_b, "unit": "TFLOP/s", "frac": achieved / peak_b,
                 "traffic": per_point * n if per_point is not None else None,
                 "peak_source": f"{src} bf16_tflops (burst: the timed region is a few milliseconds at full clock)",
@@ -593,12 +612,13 @@ def roofline_block(bench, r, fp32_tables):
         bytes_per_point = w["bytes"] + (w.get("gather_bytes", 0) if fp32_tables else 0)   # fp32 rows are twice as wide
         achieved = bytes_per_point * n / (kernel_ms * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "peak_source": f"{src} hbm_gbs", "kernel_ms": kernel_ms,
+                "traffic": traffic["all"] * n if "all" in traffic else None, "peak_source": f"{src} hbm_gbs", "kernel_ms": kernel_ms,
                 "algorithmic_bytes_per_point": bytes_per_point,
                 "scope": "all kernels of one step (the step is a chain of kernels; `kernels` lists each one's share)"}
     if r["kernels"]:
         name, k = max(r["kernels"].items(), key=lambda kv: kv[1]["ms_per_step"])
-        roof["dominant_kernel"] = {"name": name, "ms_per_step": k["ms_per_step"], "share": k["share"]}
+        roof["dominant_kernel"] = {"name": name, "ms_per_step": k["ms_per_step"], "share": k["share"],
+                                   "traffic": traffic[name] * n if name in traffic else None}
     return roof
 
 

@@ -1,8 +1,8 @@
 // Level-major encoding pass for networks whose grid tables do not fit in L2.
 //
 // When the gather runs inside the fused kernel, every warp walks through all levels of its own points, so at any moment
-// the SMs touch all tables at once: with tables far larger than the 126 MB L2 (BASELINE configuration 5: 12 hashed
-// levels of 2^22 rows) nearly every corner fetch is a random 32-byte DRAM sector. This pass reorders the work instead
+// the SMs touch all tables at once: with tables far larger than the 126 MB L2 (a 4-D grid of 16 levels of which 12 are hashed
+// tables of 2^22 rows) nearly every corner fetch is a random 32-byte DRAM sector. This pass reorders the work instead
 // of the data: the encodings of a chunk of points are computed one level at a time by the whole GPU (blockIdx.y =
 // level, the slow grid dimension), so the table of the level being processed (32 MB in fp16) stays resident in L2 and
 // corner fetches hit it there. The features go to level-major planes ([level][point][F] halfs, coalesced 4/8/16-byte

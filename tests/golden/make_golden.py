@@ -62,7 +62,7 @@ MLP_CASES = {
     # ... uneven widths as tests_cpp/test_against_eigen2.cpp:17-46 (19->16->16, 16->16->23, 20->16->24) ...
     "uneven_19_16_16": identity_cfg(19, [16, 16], ["identity", "identity"], [False, False]),
     "uneven_20_16_24": identity_cfg(20, [16, 24], ["relu", "sine"], [False, False]),
-    # ... and what the BASELINE configurations add: bias, relu/sine, 64 wide
+    # ... and what the benchmark configurations add: bias, relu/sine, 64 wide
     "config1": identity_cfg(3, [16, 1], ["relu", "relu"], [False, False]),
     "config2": identity_cfg(3, [64, 64, 64, 64, 1], ["relu", "celu", "sine", "relu", "identity"], [True] * 5),
 }

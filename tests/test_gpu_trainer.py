@@ -13,7 +13,7 @@ import specs
 pytestmark = pytest.mark.gpu
 
 
-def _target(x):   # smooth analytic target of BASELINE config 3
+def _target(x):   # smooth analytic target for the 3-D hash-grid training cases
     return (np.sin(8 * x[:, 0]) * np.cos(6 * x[:, 1]) * np.sin(4 * x[:, 2])).astype(np.float32)[:, None]
 
 

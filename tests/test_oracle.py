@@ -77,13 +77,13 @@ def test_padding_and_layout_rules():
     assert [(l.channels_in, l.channels_out) for l in s.layers] == [(32, 32), (32, 32)]      # hidden 17 -> 32 on both sides
     assert [l.weights_start for l in s.layers] == [0, 1024] and [l.bias_start for l in s.layers] == [2048, 2080]
     assert s.num_parameters == 2112
-    # parameter counts of the five BASELINE configurations
+    # parameter counts of the five benchmark configurations
     counts = [oracle.parse_spec(c).num_parameters for c in (specs.config1(), specs.config2(), specs.config3(), specs.config4(), specs.config5())]
     assert counts == [512, 14608, 7312, 15840, 43408]
 
 
 def test_level_tables():
-    """Level tables of the BASELINE grids (double-precision exp/log/pow/floor, src_cpp/src/encoding_hashgrid.cpp:64-96)."""
+    """Level tables of the benchmark grids (double-precision exp/log/pow/floor, src_cpp/src/encoding_hashgrid.cpp:64-96)."""
     lv, n = oracle.grid_levels(4, 16, 4, 22, 16, 2489)
     assert [l.resolution for l in lv] == [16, 22, 31, 43, 61, 86, 120, 168, 236, 330, 462, 647, 907, 1269, 1777, 2489]
     assert [l.hashed for l in lv] == [False] * 4 + [True] * 12 and n == 219895048
