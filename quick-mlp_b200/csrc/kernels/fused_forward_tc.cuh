@@ -4,7 +4,10 @@
 // src_cpp/include/qmlp/kernels/network_forward.cuh:34-114, and Layer::inference, kernels/layer.cuh:101-181), different
 // machine mapping:
 //   * one persistent CTA per SM; all weight matrices are staged once in shared memory in the K-major, 128-byte
-//     swizzled operand layout the tensor core reads through a shared-memory descriptor;
+//     swizzled operand layout the tensor core reads through a shared-memory descriptor. The staging is done by the
+//     tensor memory accelerator: one thread issues a tiled bulk copy (cp.async.bulk.tensor.2d, 128-byte swizzle) per
+//     weight matrix and 64-wide K block through tensor maps the launcher encodes over the caller's parameter vector,
+//     all onto one mbarrier; no cluster multicast, the source is this GPU's own memory;
 //   * the CTA consists of 1, 2, 3, 4 or 8 warpgroups of 128 threads (as many as shared and tensor memory allow for
 //     the spec's widths). A warpgroup owns one or two tile slots; a slot is one
 //     tile of 128 points in flight: an activation operand buffer in shared memory plus an fp32 accumulator in tensor
@@ -17,6 +20,7 @@
 // Every mbarrier wait is bounded, and every stage ends in a warpgroup-wide vote: on a timeout the whole warpgroup leaves
 // together, the CTA drains, tensor memory is released and the kernel reports through LaunchArgs::status.
 #pragma once
+#include <cuda.h>   // CUtensorMap and its enums; the encoder itself is fetched from the driver at run time
 #include "fused_network.cuh"
 #include "grid_planes.cuh"
 
@@ -52,6 +56,16 @@ __device__ __forceinline__ bool warpgroup_vote(int barrierId, bool pred)
     asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %2, 0;\n\tbar.red.and.pred q, %1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
                  : "=r"(r) : "r"(barrierId), "r"(static_cast<uint32_t>(pred)) : "memory");
     return r != 0;
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// tiled bulk copy global -> shared of the box at (x, y) of a 2-D tensor map; completes on the mbarrier
+__device__ __forceinline__ void tma_load_2d(uint32_t dstSmem, const void* tensorMap, int x, int y, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dstSmem), "l"(reinterpret_cast<uint64_t>(tensorMap)), "r"(x), "r"(y), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -199,8 +213,15 @@ struct TcLayout {
     __host__ __device__ static constexpr int aStart() { return weightBytes(); }
     __host__ __device__ static constexpr int biasStart() { return aStart() + slots() * aBytes(); }
     __host__ __device__ static constexpr int barStart() { return (biasStart() + biasBytes() + 127) / 128 * 128; }
-    // 8 mbarriers of 8 bytes, the TMEM base word and the abort flag, 1 KB alignment slack
+    // 8 slot mbarriers of 8 bytes, the TMEM base word, the abort flag, the weight-staging mbarrier, 1 KB alignment slack
     __host__ __device__ static constexpr int totalBytes() { return barStart() + 8 * 8 + 64 + 1024; }
+    // bytes the bulk copies of all weight matrices deliver (whole boxes: columns past Cin arrive as zeros)
+    __host__ __device__ static constexpr int weightCopyBytes()
+    {
+        int b = 0;
+        for (int i = 0; i < NL; ++i) b += wBytes(i);
+        return b;
+    }
 };
 
 // byte offset of element (row, k) of a K-major block of 16 halfs per row in the un-swizzled canonical layout:
@@ -218,20 +239,35 @@ __device__ __forceinline__ uint64_t umma_desc_k16_noswizzle(uint32_t smemAddr)
            | (1ull << 46);                                    // descriptor version (sm_100); layout type 0 = no swizzle
 }
 
-// weights of layer L -> swizzled K-major operand in shared memory (whole CTA); bias -> first K column of its block
+// One tensor map per weight matrix: the (Cout, Cin) row-major fp16 block of the caller's parameter vector as a 2-D
+// tensor, box = 64 halfs along K (one 128-byte swizzled row) x Cout rows.
+template <class Spec>
+struct TcWeightMaps {
+    CUtensorMap m[Spec::NUM_LAYERS];
+};
+
+// issued by one thread: every weight matrix, K block by K block, into the operand layout (rows 128 bytes apart, the
+// 16-byte chunks of a row xor-swizzled with the row index: exactly what sw128_offset describes)
 template <class Spec, int L>
-__device__ __forceinline__ void tc_stage_weights(const LaunchArgs& p, unsigned char* sW, unsigned char* sBias)
+__device__ __forceinline__ void tc_issue_weight_copies(const TcWeightMaps<Spec>& maps, uint32_t sW, uint32_t bar)
 {
     if constexpr (L < Spec::NUM_LAYERS) {
         using TL = TcLayout<Spec>;
-        constexpr int CIN = Spec::CIN[L], COUT = Spec::COUT[L];
-        constexpr int CH = CIN / 8;
-        const __half* gW = p.weights + Spec::WOFF[L];
-        unsigned char* dst = sW + TL::wOffset(L);
-        for (int i = threadIdx.x; i < COUT * CH; i += blockDim.x) {
-            const int r = i / CH, c = i % CH;
-            *reinterpret_cast<uint4*>(dst + sw128_offset<COUT>(r, c)) = *reinterpret_cast<const uint4*>(gW + r * CIN + c * 8);
-        }
+        constexpr int COUT = Spec::COUT[L], KB = TL::kBlocks(L), OFF = TL::wOffset(L);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+            tma_load_2d(sW + OFF + kb * COUT * 128, &maps.m[L], kb * 64, 0, bar);
+        tc_issue_weight_copies<Spec, L + 1>(maps, sW, bar);
+    }
+}
+
+// bias of layer L -> first K column of its block (whole CTA)
+template <class Spec, int L>
+__device__ __forceinline__ void tc_stage_bias(const LaunchArgs& p, unsigned char* sBias)
+{
+    if constexpr (L < Spec::NUM_LAYERS) {
+        using TL = TcLayout<Spec>;
+        constexpr int COUT = Spec::COUT[L];
         if constexpr (Spec::BOFF[L] >= 0) {
             unsigned char* bb = sBias + TL::biasOffset(L);
             for (int i = threadIdx.x; i < COUT * 16; i += blockDim.x) {
@@ -239,7 +275,7 @@ __device__ __forceinline__ void tc_stage_weights(const LaunchArgs& p, unsigned c
                 *reinterpret_cast<__half*>(bb + bias_block_offset(r, k)) = k == 0 ? p.weights[Spec::BOFF[L] + r] : __ushort_as_half(0);
             }
         }
-        tc_stage_weights<Spec, L + 1>(p, sW, sBias);
+        tc_stage_bias<Spec, L + 1>(p, sBias);
     }
 }
 
@@ -398,7 +434,7 @@ __device__ __forceinline__ bool tc_run_stages(const LaunchArgs& p, TcSlot (&sl)[
 
 template <class Spec, bool PLANES>
 __global__ void __launch_bounds__(TcLayout<Spec>::warpgroups() * 128, 1)
-fused_forward_tc_kernel(const __grid_constant__ LaunchArgs p)
+fused_forward_tc_kernel(const __grid_constant__ LaunchArgs p, const __grid_constant__ TcWeightMaps<Spec> weightMaps)
 {
     using TL = TcLayout<Spec>;
     constexpr int SLOTS = TL::slots();
@@ -413,10 +449,17 @@ fused_forward_tc_kernel(const __grid_constant__ LaunchArgs p)
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TL::barStart());   // one per slot
     uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 8);
     int* abortFlag = reinterpret_cast<int*>(tmemSlot + 1);
+    uint64_t* weightBar = reinterpret_cast<uint64_t*>(tmemSlot + 4);
 
     const int warp = threadIdx.x >> 5;
 
-    tc_stage_weights<Spec, 0>(p, sW, sBias);
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(weightBar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_expect_tx(smem_u32(weightBar), TL::weightCopyBytes());
+        tc_issue_weight_copies<Spec, 0>(weightMaps, smem_u32(sW), smem_u32(weightBar));
+    }
+    tc_stage_bias<Spec, 0>(p, sBias);
     for (int i = threadIdx.x; i < TC_TILE * 16; i += blockDim.x)   // constant A operand of the bias MMA: every row = [1, 0, ..., 0]
         *reinterpret_cast<__half*>(sBias + bias_block_offset(i >> 4, i & 15)) = (i & 15) == 0 ? __ushort_as_half(0x3C00) : __ushort_as_half(0);
     if (threadIdx.x == 0) {
@@ -428,11 +471,13 @@ fused_forward_tc_kernel(const __grid_constant__ LaunchArgs p)
         tmem_alloc(smem_u32(tmemSlot), TL::tmemCols());
         tmem_relinquish();
     }
-    fence_proxy_async();   // staged weights -> visible to the tensor core
+    fence_proxy_async();   // bias blocks written by the threads -> visible to the tensor core
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmemBase = *tmemSlot;
+    // the weights have arrived when the staging mbarrier completes its first phase (bounded wait like all others)
+    const bool weightsIn = __all_sync(0xffffffffu, mbar_wait(smem_u32(weightBar), 0));
 
     // tile i of this CTA's sequence (global tile blockIdx.x + i * gridDim.x) goes to slot i % SLOTS
     const long long numTiles = (p.numel + TC_TILE - 1) / TC_TILE;
@@ -457,7 +502,7 @@ fused_forward_tc_kernel(const __grid_constant__ LaunchArgs p)
         sl[j].taddr = sl[j].dTmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
         sl[j].fullParity = 0;
     }
-    bool ok = true;
+    bool ok = weightsIn;
     for (long long i = static_cast<long long>(wg) * SPW; i < myTiles && ok; i += SLOTS) {
 #pragma unroll
         for (int j = 0; j < SPW; ++j) {
@@ -487,6 +532,11 @@ struct TcLaunchers {
         constexpr int threads = TL::warpgroups() * 128;
         static DeviceOnce once;   // function attributes are per device
         auto k = fused_forward_tc_kernel<Spec, PLANES>;
+        TcWeightMaps<Spec> maps;
+        {
+            const cudaError_t e = encodeWeightMaps(a.weights, maps);
+            if (e != cudaSuccess) return e;
+        }
         {
             const cudaError_t e = once.run([&] { return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
             if (e != cudaSuccess) return e;
@@ -494,8 +544,36 @@ struct TcLaunchers {
         const long long tiles = (a.numel + TC_TILE - 1) / TC_TILE;
         long long blocks = tiles < a.numSMs ? tiles : a.numSMs;
         if (blocks < 1) blocks = 1;
-        k<<<static_cast<unsigned>(blocks), threads, smem, s>>>(a);
+        k<<<static_cast<unsigned>(blocks), threads, smem, s>>>(a, maps);
         return cudaGetLastError();
+    }
+    // Tensor maps over the weight matrices of the bound parameter vector. Encoding is host arithmetic (no driver call
+    // touches the device), a microsecond per matrix; the maps travel as a kernel parameter.
+    static cudaError_t encodeWeightMaps(const __half* weights, TcWeightMaps<Spec>& maps)
+    {
+        using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                      const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+        static const EncodeFn encode = [] {
+            void* fn = nullptr;
+            cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
+            if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found) != cudaSuccess || found != cudaDriverEntryPointSuccess)
+                fn = nullptr;
+            return reinterpret_cast<EncodeFn>(fn);
+        }();
+        if (encode == nullptr) return cudaErrorNotSupported;
+        if ((reinterpret_cast<uintptr_t>(weights) & 15u) != 0) return cudaErrorMisalignedAddress;
+        for (int l = 0; l < Spec::NUM_LAYERS; ++l) {
+            const cuuint64_t dims[2] = {static_cast<cuuint64_t>(Spec::CIN[l]), static_cast<cuuint64_t>(Spec::COUT[l])};
+            const cuuint64_t strides[1] = {static_cast<cuuint64_t>(Spec::CIN[l]) * 2};   // bytes between rows
+            const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(Spec::COUT[l])};       // a narrower matrix is zero-filled up to 64
+            const cuuint32_t elemStrides[2] = {1, 1};
+            void* base = const_cast<__half*>(weights + Spec::WOFF[l]);
+            if (encode(&maps.m[l], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+                return cudaErrorInvalidValue;
+        }
+        return cudaSuccess;
     }
     static cudaError_t inference(const LaunchArgs& a, cudaStream_t s) { return run<false>(a, s); }
     static cudaError_t inferencePlanes(const LaunchArgs& a, cudaStream_t s) { return run<true>(a, s); }
