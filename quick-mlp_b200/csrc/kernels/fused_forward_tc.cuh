@@ -67,6 +67,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dstSmem, const void* tensor
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dstSmem), "l"(reinterpret_cast<uint64_t>(tensorMap)), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+// stores through 32-bit shared-window addresses (one register per address instead of a generic pointer's two)
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) { asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
+__device__ __forceinline__ void sts16(uint32_t addr, __half v)
+{
+    asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(__half_as_ushort(v)) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -283,9 +293,10 @@ __device__ __forceinline__ void tc_stage_bias(const LaunchArgs& p, unsigned char
 template <class Spec, int L>
 // The descriptors differ from call to call only in the 14-bit start-address field (low word, 16-byte units), so the
 // issuing thread keeps three base descriptors and adds compile-time offsets.
-__device__ __forceinline__ void tc_issue_layer(uint64_t aDesc0, uint64_t wDesc0, uint64_t biasDesc0, uint32_t dTmem, uint32_t fullBar)
+__device__ __forceinline__ void tc_issue_layer(uint32_t aSmem, uint32_t wSmem, uint32_t biasSmem, uint32_t dTmem, uint32_t fullBar)
 {
     using TL = TcLayout<Spec>;
+    const uint64_t aDesc0 = umma_desc_sw128(aSmem), wDesc0 = umma_desc_sw128(wSmem), biasDesc0 = umma_desc_k16_noswizzle(biasSmem);
     constexpr int CIN = Spec::CIN[L], COUT = Spec::COUT[L];
     constexpr uint32_t idesc = umma_idesc_f16(TC_TILE, COUT);
 #pragma unroll
@@ -301,9 +312,7 @@ __device__ __forceinline__ void tc_issue_layer(uint64_t aDesc0, uint64_t wDesc0,
 
 // ---- one warpgroup, one thread per point row -----------------------------------------------------------------------
 struct TcSlot {                 // per-thread view of one tile slot
-    unsigned char* aBuf;        // activation operand buffer of the slot
-    uint64_t aDesc0;            // operand descriptor of its first K step
-    uint32_t dTmem;             // TMEM address of the slot's accumulator (lane 0)
+    uint32_t aRow;              // shared-window address of this thread's row of the slot's activation operand buffer
     uint32_t taddr;             // TMEM address of this thread's accumulator row
     uint32_t fullBar;           // mbarrier the MMAs of the slot commit to
     uint32_t fullParity;
@@ -311,24 +320,25 @@ struct TcSlot {                 // per-thread view of one tile slot
     bool active;                // the slot has a tile in this round
 };
 
+// byte offset of 16-byte chunk `chunk` inside a row of the operand whose row base (row * 128) is known: the K block's
+// base plus the chunk position xor-swizzled with the row
+__device__ __forceinline__ uint32_t sw128_row_offset(int row, int chunk)
+{
+    return static_cast<uint32_t>((chunk >> 3) * (TC_TILE * 128) + (((chunk & 7) ^ (row & 7)) << 4));
+}
+
 struct TcRowWriter {   // encoded features of one point -> swizzled row of the A operand
-    unsigned char* aBuf;
+    uint32_t aRow;
     int row;
-    __device__ __forceinline__ void operator()(int c, float v) const
-    {
-        *reinterpret_cast<__half*>(aBuf + sw128_offset<TC_TILE>(row, c >> 3) + (c & 7) * 2) = __float2half(v);
-    }
-    __device__ __forceinline__ void half(int c, __half v) const
-    {
-        *reinterpret_cast<__half*>(aBuf + sw128_offset<TC_TILE>(row, c >> 3) + (c & 7) * 2) = v;
-    }
+    __device__ __forceinline__ void operator()(int c, float v) const { sts16(aRow + sw128_row_offset(row, c >> 3) + (c & 7) * 2, __float2half(v)); }
+    __device__ __forceinline__ void half(int c, __half v) const { sts16(aRow + sw128_row_offset(row, c >> 3) + (c & 7) * 2, v); }
     __device__ __forceinline__ void half2(int c, uint32_t v) const   // channels c, c + 1
     {
         if (c & 1) {
             half(c, __ushort_as_half(static_cast<unsigned short>(v & 0xffffu)));
             half(c + 1, __ushort_as_half(static_cast<unsigned short>(v >> 16)));
         } else {
-            *reinterpret_cast<uint32_t*>(aBuf + sw128_offset<TC_TILE>(row, c >> 3) + (c & 7) * 2) = v;
+            sts32(aRow + sw128_row_offset(row, c >> 3) + (c & 7) * 2, v);
         }
     }
 };
@@ -336,8 +346,7 @@ struct TcRowWriter {   // encoded features of one point -> swizzled row of the A
 // Stage 0: encode the point into the layer-0 operand. Stage L+1: epilogue of layer L. Each stage but the last ends
 // by launching the MMAs of the next layer. Returns false, for the whole warpgroup at once, when a wait timed out.
 template <class Spec, int ST, bool PLANES>
-__device__ __forceinline__ bool tc_stage(const LaunchArgs& p, TcSlot& sl, uint64_t biasDesc0, uint64_t wDesc0, int row,
-                                         int barrierId, bool issuer)
+__device__ __forceinline__ bool tc_stage(const LaunchArgs& p, TcSlot& sl, uint32_t smemBase, int row, int barrierId, bool issuer)
 {
     constexpr int NL = Spec::NUM_LAYERS;
     bool ok = true;
@@ -345,13 +354,13 @@ __device__ __forceinline__ bool tc_stage(const LaunchArgs& p, TcSlot& sl, uint64
         constexpr int CIN0 = Spec::CIN[0];
         // zero padding up to CIN0 and zero rows past the end of the batch
 #pragma unroll
-        for (int c = 0; c < CIN0 / 8; ++c) *reinterpret_cast<uint4*>(sl.aBuf + sw128_offset<TC_TILE>(row, c)) = make_uint4(0, 0, 0, 0);
+        for (int c = 0; c < CIN0 / 8; ++c) sts128(sl.aRow + sw128_row_offset(row, c), 0, 0, 0, 0);
         if (sl.gRow < p.numel) {
             if constexpr (PLANES) {
-                read_planes_point<Spec, 0>(p, sl.gRow, TcRowWriter{sl.aBuf, row});
+                read_planes_point<Spec, 0>(p, sl.gRow, TcRowWriter{sl.aRow, row});
             } else {
                 RowReader in{p.input + sl.gRow * p.inS0, p.inS1};
-                encode_point<Spec, 0>(p, in, TcRowWriter{sl.aBuf, row});
+                encode_point<Spec, 0>(p, in, TcRowWriter{sl.aRow, row});
             }
         }
     } else {
@@ -385,8 +394,8 @@ __device__ __forceinline__ bool tc_stage(const LaunchArgs& p, TcSlot& sl, uint64
                     const int chunk = (c0 + g * 16) / 8;
                     if constexpr (!LAST) {
                         // row of the next layer's A operand: two 16-byte chunks
-                        *reinterpret_cast<uint4*>(sl.aBuf + sw128_offset<TC_TILE>(row, chunk)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                        *reinterpret_cast<uint4*>(sl.aBuf + sw128_offset<TC_TILE>(row, chunk + 1)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        sts128(sl.aRow + sw128_row_offset(row, chunk), packed[0], packed[1], packed[2], packed[3]);
+                        sts128(sl.aRow + sw128_row_offset(row, chunk + 1), packed[4], packed[5], packed[6], packed[7]);
                     } else if (sl.gRow < p.numel) {
                         // first NUM_OUTPUTS channels -> fp32 (kernels/network_forward.cuh:103-111)
 #pragma unroll
@@ -408,8 +417,10 @@ __device__ __forceinline__ bool tc_stage(const LaunchArgs& p, TcSlot& sl, uint64
     ok = warpgroup_vote(barrierId, ok);
     if constexpr (ST < NL) {
         if (ok && issuer) {
+            // the issuing thread's row is the first of its warp: its addresses minus the row / lane parts are the slot's
             tc_fence_after();
-            tc_issue_layer<Spec, ST>(sl.aDesc0, wDesc0, biasDesc0, sl.dTmem, sl.fullBar);
+            tc_issue_layer<Spec, ST>(sl.aRow - row * 128, smemBase, smemBase + TcLayout<Spec>::biasStart(),
+                                     sl.taddr & 0x0000ffffu, sl.fullBar);
         }
     }
     return ok;
@@ -417,16 +428,15 @@ __device__ __forceinline__ bool tc_stage(const LaunchArgs& p, TcSlot& sl, uint64
 
 // all stages of up to SPW tiles, interleaved stage by stage
 template <class Spec, int ST, int SPW, bool PLANES>
-__device__ __forceinline__ bool tc_run_stages(const LaunchArgs& p, TcSlot (&sl)[SPW], uint64_t biasDesc0, uint64_t wDesc0, int row,
-                                              int barrierId, bool issuer)
+__device__ __forceinline__ bool tc_run_stages(const LaunchArgs& p, TcSlot (&sl)[SPW], uint32_t smemBase, int row, int barrierId, bool issuer)
 {
     if constexpr (ST <= Spec::NUM_LAYERS) {
 #pragma unroll
         for (int j = 0; j < SPW; ++j)
             if (sl[j].active) {   // uniform over the warpgroup
-                if (!tc_stage<Spec, ST, PLANES>(p, sl[j], biasDesc0, wDesc0, row, barrierId, issuer)) return false;
+                if (!tc_stage<Spec, ST, PLANES>(p, sl[j], smemBase, row, barrierId, issuer)) return false;
             }
-        return tc_run_stages<Spec, ST + 1, SPW, PLANES>(p, sl, biasDesc0, wDesc0, row, barrierId, issuer);
+        return tc_run_stages<Spec, ST + 1, SPW, PLANES>(p, sl, smemBase, row, barrierId, issuer);
     } else {
         return true;
     }
@@ -444,7 +454,6 @@ fused_forward_tc_kernel(const __grid_constant__ LaunchArgs p, const __grid_const
     // the swizzled operand layout needs 1024-byte alignment of every operand base
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~static_cast<uintptr_t>(1023));
     unsigned char* sW = smem;
-    unsigned char* sA = smem + TL::aStart();
     unsigned char* sBias = smem + TL::biasStart();   // [ones block | bias block per layer]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TL::barStart());   // one per slot
     uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 8);
@@ -480,36 +489,36 @@ fused_forward_tc_kernel(const __grid_constant__ LaunchArgs p, const __grid_const
     const bool weightsIn = __all_sync(0xffffffffu, mbar_wait(smem_u32(weightBar), 0));
 
     // tile i of this CTA's sequence (global tile blockIdx.x + i * gridDim.x) goes to slot i % SLOTS
-    const long long numTiles = (p.numel + TC_TILE - 1) / TC_TILE;
-    const long long firstTile = blockIdx.x;
-    const long long stride = gridDim.x;
-    const long long myTiles = firstTile < numTiles ? (numTiles - firstTile + stride - 1) / stride : 0;
+    // (32-bit tile counters: a launch holds fewer than 2^31 tiles of 128 points)
+    const int numTiles = static_cast<int>((p.numel + TC_TILE - 1) / TC_TILE);
+    const int firstTile = blockIdx.x;
+    const int stride = gridDim.x;
+    const int myTiles = firstTile < numTiles ? (numTiles - firstTile + stride - 1) / stride : 0;
 
     const int wg = warp >> 2;
     const int row = threadIdx.x & 127;                       // point row inside the tile = TMEM lane
     // the MMA-issuing thread of warpgroup wg sits in its warp (wg % 4), so the four issuers of a CTA run on four
     // different SM sub-partitions instead of all on the first one
     const bool issuer = row == (wg & 3) * 32;
-    const uint64_t wDesc0 = umma_desc_sw128(smem_u32(sW)), biasDesc0 = umma_desc_k16_noswizzle(smem_u32(sBias));
+    const uint32_t smemBase = smem_u32(smem);   // = the weight operands; everything else sits at fixed offsets from it
     TcSlot sl[SPW];
 #pragma unroll
     for (int j = 0; j < SPW; ++j) {
         const int s = wg * SPW + j;
-        sl[j].aBuf = sA + s * TL::aBytes();
-        sl[j].aDesc0 = umma_desc_sw128(smem_u32(sl[j].aBuf));
+        sl[j].aRow = smemBase + TL::aStart() + s * TL::aBytes() + row * 128;
         sl[j].fullBar = smem_u32(bars + s);
-        sl[j].dTmem = tmemBase + s * TL::accCols();
-        sl[j].taddr = sl[j].dTmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+        // (the allocation's lane field is 0, so the lane offset can be taken off again by masking)
+        sl[j].taddr = tmemBase + s * TL::accCols() + (static_cast<uint32_t>((warp & 3) * 32) << 16);
         sl[j].fullParity = 0;
     }
     bool ok = weightsIn;
-    for (long long i = static_cast<long long>(wg) * SPW; i < myTiles && ok; i += SLOTS) {
+    for (int i = wg * SPW; i < myTiles && ok; i += SLOTS) {
 #pragma unroll
         for (int j = 0; j < SPW; ++j) {
             sl[j].active = i + j < myTiles;
-            sl[j].gRow = (firstTile + (i + j) * stride) * TC_TILE + row;
+            sl[j].gRow = (firstTile + static_cast<long long>(i + j) * stride) * TC_TILE + row;
         }
-        ok = tc_run_stages<Spec, 0, SPW, PLANES>(p, sl, biasDesc0, wDesc0, row, 1 + wg, issuer);
+        ok = tc_run_stages<Spec, 0, SPW, PLANES>(p, sl, smemBase, row, 1 + wg, issuer);
     }
     if (!ok) *abortFlag = 1;
     // drain: every warpgroup reaches this point (all waits are bounded), then tensor memory is released
