@@ -58,7 +58,7 @@ def measured_traffic_per_point():
 
 KERNEL_NAMES = {0: "inference", 1: "forward_stash", 2: "forward_loss", 3: "backward", 4: "wgrad", 9: "encode_planes",
                 10: "inference_planes", 11: "scatter_planes", 12: "forward_loss_planes", 13: "sort_points",
-                14: "backward_wgrad", 100: "adam", 101: "refresh_half"}
+                15: "scatter_sorted", 100: "adam", 101: "refresh_half"}
 
 
 def load_peaks():
