@@ -277,7 +277,8 @@ QMLP_API int qmlp_trainer_gradients(qmlp_trainer_t* tr, const qmlp_tensor_t* inp
  * table gradients are scattered by a kernel of their own (qmlp_trainer_scatter_levels > 0): parts = 4 runs forward and
  * backward and leaves the adjoint feature planes in the workspace; parts = 8 | first << 8 | end << 16 then scatters
  * the grid levels [first, end) (numbered over all grids as qmlp_trainer_scatter_levels lists them), after which their
- * part of the gradient buffer is final; every level must be scattered exactly once before qmlp_trainer_update. */
+ * part of the gradient buffer is final; every level must be scattered exactly once before qmlp_trainer_update. After
+ * part 4 the level ranges and part 2 may follow in any order. */
 QMLP_API int qmlp_trainer_gradients_part(qmlp_trainer_t* tr, const qmlp_tensor_t* input, const qmlp_tensor_t* target,
                                          int64_t global_points, void* workspace, size_t workspace_bytes,
                                          float* loss_sum, int parts, qmlp_stream_t stream);

@@ -140,13 +140,13 @@ class FusedTrainer:
         vector. The element ranges tile [first table segment, fused_count).
 
         The fine levels go first, ``level_group_size`` levels per launch from the top, so that the large slices (a
-        hashed level is a full-size table) are on the wire early, each under the scatter launch that follows it; the
-        coarsest level is a launch of its own at the very end, after the layers' weight-gradient kernel
-        (``_wgrad_position`` = how many launches precede that kernel): the second-to-last all-reduce runs under the
-        weight-gradient kernel and the only one left without cover is that of the smallest level. Few large groups beat
-        many small ones: every all-reduce occupies SMs the scatter wants, for as long as it runs, and a launch more is
-        a tail more (eight GPUs, 16 levels: 1.43 ms per step with 8 levels per launch, 1.45 with 6, 1.44-1.48 with 4,
-        1.50 with 3). [] when the scatter is not a kernel of its own, or on one rank."""
+        hashed level is a full-size table) are on the wire early, under the launches that follow; the layers'
+        weight-gradient kernel runs before the last two launches (``_wgrad_position`` = how many launches precede it),
+        and the coarsest level is a launch of its own at the very end, so the last all-reduce is that of the smallest
+        level. Few large groups beat many small ones: every all-reduce occupies SMs the scatter wants, for as long as
+        it runs, and a launch more is a tail more (eight GPUs, 16 levels: 1.43 ms per step with 8 levels per launch,
+        1.45 with 6, 1.44-1.48 with 4, 1.50 with 3; with the weight-gradient kernel before the last launch only,
+        1.48 with 8 and 1.51 with 6). [] when the scatter is not a kernel of its own, or on one rank."""
         key = ("groups", world_size, self.level_group_size)
         cached = getattr(self, "_groups_cache", None)
         if cached is not None and cached[0] == key:
@@ -165,7 +165,7 @@ class FusedTrainer:
             if hi > 1:
                 ranges.append((1, hi))
             ranges.append((0, 1))
-            self._wgrad_position = len(ranges) - 1   # the weight-gradient kernel runs before the last launch
+            self._wgrad_position = max(len(ranges) - 2, 0)   # the weight-gradient kernel runs before the last two launches
             first_table = min(s for s in self.backend.segments[1:] if s >= 0)
             for lo, hi in ranges:
                 begin = first_table if lo == 0 else levels[lo][0]
