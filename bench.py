@@ -107,8 +107,9 @@ def config_block(key, w, n, world, fp32_tables):
            "grid_tables": "fp32" if fp32_tables else "fp16",
            "l2": "rotating input/output buffer sets and the step's scratch exceed the 126 MB L2"}
     if w["mode"] == "train":
-        cfg["parallelism"] = (f"dp{world}, all-reduce (NCCL, NCCL_NVLS_ENABLE={os.environ.get('NCCL_NVLS_ENABLE', '0')}) of the fused "
-                              "gradient vector inside the timed step") if world > 1 else "dp1"
+        nvls = os.environ.get("NCCL_NVLS_ENABLE", "0" if world >= 8 else "default")
+        cfg["parallelism"] = (f"dp{world}, all-reduce (NCCL, NCCL_NVLS_ENABLE={nvls}) of the fused gradient vector inside "
+                              "the timed step") if world > 1 else "dp1"
     else:
         cfg["parallelism"] = f"replicas x{world}, points sharded, no data-path collective"
     return cfg
@@ -646,6 +647,18 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
 
+    # A run that has produced no line after a quarter of an hour (several times what any configuration needs) ends itself
+    # instead of holding the GPUs; the timer thread fires even while the main thread waits inside a CUDA or NCCL call.
+    import threading
+
+    def give_up():
+        sys.stderr.write("bench.py: no result within 900 s, giving up\n")
+        sys.stderr.flush()
+        os._exit(124)
+    watchdog = threading.Timer(900.0, give_up)
+    watchdog.daemon = True
+    watchdog.start()
+
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
         return
@@ -664,11 +677,14 @@ def main():
         all_cores = None
     numa = bind_to_gpu_numa_node(torch, local_rank)
     if world > 1:
-        # The data-parallel step runs its all-reduces underneath kernels that are bound by the L2; NCCL's ring kernels
-        # disturb them less than its NVSwitch-multicast (NVLS) ones: 1.47 against 1.54 ms per step on eight GPUs, 1.36
-        # against 1.39 on four. A user's own setting wins.
-        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        dist.init_process_group("nccl", device_id=dev)
+        # The data-parallel step runs its all-reduces underneath kernels that are bound by the L2; on eight GPUs NCCL's
+        # ring kernels disturb them less than its NVSwitch-multicast (NVLS) ones: 1.47 against 1.54 ms per step. (Four
+        # GPUs: 1.36 against 1.39; left at NCCL's default there.) A user's own setting wins.
+        if world >= 8:
+            os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        # a collective that does not complete within three minutes ends the run with an error instead of hanging it
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     load_library()
     bindings.QuickMLP.set_log_level("error")
     for item in args.tune:

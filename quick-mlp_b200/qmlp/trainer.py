@@ -105,7 +105,7 @@ class FusedTrainer:
         self.backend.bind(self.master, self.gradient, self.adam_m, self.adam_v, self.half)
         self.step_count = 0
         self.process_group = process_group
-        self.level_group_size = 8      # grid levels per scatter launch of a data-parallel step (0: one launch)
+        self.level_group_size = 3      # grid levels per scatter launch of a data-parallel step (0: one launch)
 
     # -- parameter access ---------------------------------------------------------------------------------------------
     def segment(self, buffer: torch.Tensor, index: int) -> Optional[torch.Tensor]:
@@ -135,42 +135,26 @@ class FusedTrainer:
                 dist.broadcast(t, src=src, group=self.process_group)
 
     def _level_groups(self, world_size: int):
-        """[(first level, end level, first element, end element)] in launch order: the launches the table-gradient
-        scatter is cut into for a data-parallel step, each followed by the all-reduce of its part of the gradient
-        vector. The element ranges tile [first table segment, fused_count).
-
-        The fine levels go first, ``level_group_size`` levels per launch from the top, so that the large slices (a
-        hashed level is a full-size table) are on the wire early, under the launches that follow; the layers'
-        weight-gradient kernel runs before the last two launches (``_wgrad_position`` = how many launches precede it),
-        and the coarsest level is a launch of its own at the very end, so the last all-reduce is that of the smallest
-        level. Few large groups beat many small ones: every all-reduce occupies SMs the scatter wants, for as long as
-        it runs, and a launch more is a tail more (eight GPUs, 16 levels: 1.43 ms per step with 8 levels per launch,
-        1.45 with 6, 1.44-1.48 with 4, 1.50 with 3; with the weight-gradient kernel before the last launch only,
-        1.48 with 8 and 1.51 with 6). [] when the scatter is not a kernel of its own, or on one rank."""
+        """[(first level, end level, first element, end element)]: the launches the table-gradient scatter is cut into
+        for a data-parallel step, each followed by the all-reduce of its part of the gradient vector. The element ranges
+        tile [first table segment, fused_count). Three levels per launch, the first launch takes what is left over (the
+        coarse levels are small): the last all-reduce is then short enough to hide under the weight-gradient kernel.
+        [] when the scatter is not a kernel of its own, or on one rank."""
         key = ("groups", world_size, self.level_group_size)
         cached = getattr(self, "_groups_cache", None)
         if cached is not None and cached[0] == key:
             return cached[1]
         levels = self.backend.scatter_levels() if (world_size > 1 and hasattr(self.backend, "scatter_levels")) else []
         groups = []
-        self._wgrad_position = 0
         if len(levels) >= 2 and self.level_group_size > 0:
-            count, size = len(levels), self.level_group_size
-            while (count + size - 1) // size > 4:      # at most four full-size launches
-                size += 1
-            ranges, hi = [], count
-            while hi > size:
-                ranges.append((hi - size, hi))
-                hi -= size
-            if hi > 1:
-                ranges.append((1, hi))
-            ranges.append((0, 1))
-            self._wgrad_position = max(len(ranges) - 2, 0)   # the weight-gradient kernel runs before the last two launches
+            cuts = list(range(len(levels), 0, -self.level_group_size))[::-1][-4:]      # at most four: L - 9, L - 6, L - 3, L
             first_table = min(s for s in self.backend.segments[1:] if s >= 0)
-            for lo, hi in ranges:
+            lo = 0
+            for hi in cuts:
                 begin = first_table if lo == 0 else levels[lo][0]
-                end = self.backend.fused_count if hi == count else levels[hi][0]
+                end = self.backend.fused_count if hi == len(levels) else levels[hi][0]
                 groups.append((lo, hi, begin, end))
+                lo = hi
         self._groups_cache = (key, groups)
         return groups
 
@@ -212,17 +196,15 @@ class FusedTrainer:
         groups = self._level_groups(world) if world > 1 and table_starts else []
         if groups:
             # The scatter kernel works through the grid levels in a few launches. The gradient of a level is final when
-            # its launch is: its all-reduce starts then (on the communication stream) and runs underneath the launches
-            # that follow - the remaining fine levels, the layers' weight-gradient kernel, the coarse levels.
-            first_table = min(table_starts)
+            # its launch is: its all-reduce starts then (on the communication stream) and runs underneath the scatter of
+            # the following levels, the last one underneath the layers' weight-gradient kernel.
             self.backend.gradients(x, target, global_points, self.loss_sum, parts=4)
             pending = []
-            for i, (level_begin, level_end, begin, end) in enumerate(groups):
-                if i == self._wgrad_position:
-                    self.backend.gradients(x, target, global_points, self.loss_sum, parts=2)
-                    pending.append(dist.all_reduce(self.gradient[:first_table], op=dist.ReduceOp.SUM, group=self.process_group, async_op=True))
+            for level_begin, level_end, begin, end in groups:
                 self.backend.gradients(x, target, global_points, self.loss_sum, parts=8 | (level_begin << 8) | (level_end << 16))
                 pending.append(dist.all_reduce(self.gradient[begin:end], op=dist.ReduceOp.SUM, group=self.process_group, async_op=True))
+            self.backend.gradients(x, target, global_points, self.loss_sum, parts=2)
+            dist.all_reduce(self.gradient[:groups[0][2]], op=dist.ReduceOp.SUM, group=self.process_group)
             for p in pending:
                 p.wait()
         elif world > 1 and table_starts and getattr(self.backend, "split_gradients", False):
