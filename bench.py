@@ -357,6 +357,14 @@ class Bench:
             self.dist.barrier()
         self.torch.cuda.synchronize()
 
+    def all_ranks_agree(self, flag):
+        """True only if `flag` holds on every rank (a collective at N > 1: all ranks call it the same number of times)."""
+        if self.world == 1:
+            return bool(flag)
+        t = self.torch.tensor([1 if flag else 0], device=self.dev, dtype=self.torch.int32)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MIN)
+        return bool(t.item())
+
     def max_over_ranks(self, v):
         t = self.torch.tensor([v], device=self.dev, dtype=self.torch.float64)
         if self.world > 1:
@@ -429,12 +437,17 @@ class Bench:
         step(0)
         torch.cuda.synchronize()
         if primary:
+            # Blocks of eight steps until 0.4 s have passed. Every rank must take the same number of steps (a step of the
+            # data-parallel workload contains collectives, and a rank that took one step more would leave its last
+            # all-reduces without partners): the decision to go on is taken after each block and agreed over the ranks.
             t_settle = time.perf_counter()
             i = 0
-            while time.perf_counter() - t_settle < 0.4:
-                step(i); i += 1
-                if i % 8 == 0:
-                    torch.cuda.synchronize()
+            go_on = True
+            while go_on:
+                for _ in range(8):
+                    step(i); i += 1
+                torch.cuda.synchronize()
+                go_on = self.all_ranks_agree(time.perf_counter() - t_settle < 0.4)
         for i in range(warmup):
             step(i)
         self.barrier()
