@@ -588,8 +588,12 @@ class Bench:
         dist.broadcast(h0, src=0)
         d = torch.stack([(trainer.master - m0).abs().max().double(), (trainer.half.float() - h0.float()).abs().max().double()])
         dist.all_reduce(d, op=dist.ReduceOp.MAX)
+        # (every rank has taken the same number of steps: most and fewest over the ranks)
+        c = torch.tensor([trainer.step_count, -trainer.step_count], device=self.dev, dtype=torch.int64)
+        dist.all_reduce(c, op=dist.ReduceOp.MAX)
         return {"max_abs_master_diff_vs_rank0": float(d[0].item()), "max_abs_half_copy_diff_vs_rank0": float(d[1].item()),
-                "steps_taken": int(trainer.step_count), "nccl_bytes_per_step": int(trainer.gradient.numel() * 4),
+                "steps_taken": int(trainer.step_count), "steps_taken_all_ranks": [int(-c[1].item()), int(c[0].item())],
+                "nccl_bytes_per_step": int(trainer.gradient.numel() * 4),
                 "collectives_per_step": trainer.collectives_per_step(self.world)}
 
 
