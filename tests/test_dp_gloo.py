@@ -168,6 +168,38 @@ def test_shard_points():
         assert max(sizes) - min(sizes) <= 1
 
 
+def test_level_groups_tile_the_table_gradients():
+    """Whatever the number of grid levels: the scatter launches of a data-parallel step cover every level exactly once,
+    and the slices that are all-reduced after them tile [first table element, fused_count) without gap or overlap."""
+    from qmlp.trainer import FusedTrainer
+
+    class Levels:
+        segments = [0, 7360]
+
+        def __init__(self, count):
+            self.count = count
+            self.fused_count = 7360 + 100 * count + 28   # with alignment slack after the last level
+
+        def scatter_levels(self):
+            return [(7360 + 100 * i, 7360 + 100 * (i + 1)) for i in range(self.count)]
+
+    for count in (1, 2, 3, 4, 7, 8, 9, 16, 17, 32):
+        for size in (0, 1, 3, 8):
+            tr = FusedTrainer.__new__(FusedTrainer)
+            tr.backend, tr.level_group_size = Levels(count), size
+            groups = tr._level_groups(4)
+            if count < 2 or size == 0:
+                assert groups == []
+                continue
+            assert 1 <= len(groups) <= 4
+            by_level = sorted(groups)
+            assert by_level[0][0] == 0 and by_level[-1][1] == count
+            assert all(a[1] == b[0] and a[3] == b[2] for a, b in zip(by_level, by_level[1:]))
+            assert by_level[0][2] == 7360 and by_level[-1][3] == tr.backend.fused_count
+            assert tr.collectives_per_step(4) == len(groups) + 1
+        assert FusedTrainer._level_groups(tr, 1) == []          # one rank: no groups
+
+
 @pytest.mark.timeout(300)
 def test_two_ranks_equal_one_rank(tmp_path):
     import torch.multiprocessing as mp
