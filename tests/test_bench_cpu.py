@@ -45,3 +45,30 @@ def test_reference_arm_prints_one_json_line():
     d = json.loads(lines[0])
     assert d["impl"] == "reference" and d["value"] > 0 and d["cpu_baseline"]["kind"] == "port"
     assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0
+
+
+def _agree_worker(rank, world, port, out_dir):
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    bench = _bench()
+    b = bench.Bench.__new__(bench.Bench)
+    b.torch, b.dist, b.world, b.rank, b.dev = torch, dist, world, rank, torch.device("cpu")
+    # the settling loop of a data-parallel run: a rank whose own clock says "stop" makes every rank stop
+    answers = [b.all_ranks_agree(True), b.all_ranks_agree(rank == 0), b.all_ranks_agree(False)]
+    with open(os.path.join(out_dir, f"agree{rank}.json"), "w") as f:
+        json.dump(answers, f)
+    dist.destroy_process_group()
+
+
+def test_ranks_agree_on_going_on(tmp_path):
+    import socket
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_agree_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    for rank in range(2):
+        with open(tmp_path / f"agree{rank}.json") as f:
+            assert json.load(f) == [True, False, False]
