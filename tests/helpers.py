@@ -6,7 +6,7 @@ import numpy as np
 
 import qmlp_oracle as oracle
 
-# tolerance north_star states for fp16 results: 1e-2 relative, plus the absolute floor the reference's own
+# tolerance for fp16 results: the stated target of 1e-2 relative, plus the absolute floor the reference's own
 # comparison uses (tests_py/qmlp_tests/test_network_base.py:95-96)
 RTOL, ATOL = 1e-2, 1e-3
 RTOL_WGRAD = 1e-1          # the reference's bound for weight gradients (test_network_base.py:97)

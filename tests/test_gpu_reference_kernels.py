@@ -4,7 +4,7 @@ per configuration the way FusedNetwork::compileInferenceKernel fills it and comp
 oracle/build_ref_kernels.py, runs beside this build's kernels on the same inputs and parameters.
 
 The reference kernel accumulates in half (kernels/layer.cuh:110) where this build accumulates in fp32, so the two are
-compared with north_star's tolerance |a-b| <= 1e-2 |b| + 1e-3 and both are compared with the fp32 oracle."""
+compared with the tolerance |a-b| <= 1e-2 |b| + 1e-3 (1e-2 relative is the stated target for fp16 results, 1e-3 the reference's own absolute floor) and both are compared with the fp32 oracle."""
 import json
 import os
 import sys
